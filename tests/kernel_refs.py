@@ -14,22 +14,57 @@ def embed_gather(table, ids, out=None):
     return table[ids.long()].to(torch.float32)
 
 
-def add_rmsnorm(h, delta, weight, eps, out_dtype, rows=None, out=None):
+class Scaled:
+    def __init__(self, delta, scale):
+        self.delta, self.scale = delta, float(scale)
+
+
+def add_rmsnorm(h, delta, weight, eps, out_dtype, rows=None, out=None, bias=None):
+    scale = 1.0
+    if isinstance(delta, Scaled):
+        delta, scale = delta.delta, delta.scale
     if rows is None:
         if delta is not None:
-            h += delta.to(torch.float32)
+            h += torch.tensor(scale, dtype=torch.float32) * delta.to(torch.float32)
+        if bias is not None:
+            h += bias
         x = h
     else:   # picked rows (repeats allowed): h itself stays as it is
         x = h[rows.long()]
         if delta is not None:
-            x = x + delta[rows.long()].to(torch.float32)
+            x = x + torch.tensor(scale, dtype=torch.float32) * delta[rows.long()].to(torch.float32)
+        if bias is not None:
+            x = x + bias
     ms = (x * x).mean(dim=-1, keepdim=True)
     inv = 1.0 / torch.sqrt(ms + torch.tensor(eps, dtype=torch.float32))
     return (x * weight * inv).to(out_dtype)
 
 
 def residual_add(h, delta):
-    h += delta.to(torch.float32)
+    scale = 1.0
+    if isinstance(delta, Scaled):
+        delta, scale = delta.delta, delta.scale
+    h += torch.tensor(scale, dtype=torch.float32) * delta.to(torch.float32)
+
+
+def scale_(x, factor):
+    x *= factor
+    return x
+
+
+def sigmoid_gate(x, gate, out=None):
+    res = (x.to(torch.float32) * torch.sigmoid(gate.to(torch.float32))).to(x.dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gelu_tanh(z):
+    return 0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z * z * z)))
 
 
 SWIGLU_INTERLEAVE = 64
@@ -44,13 +79,15 @@ def linear_swiglu(x, w_interleaved, out_dtype=None):
     return swiglu(linear(x, w_interleaved, out_dtype=torch.float32), interleave=64).to(out_dtype or x.dtype)
 
 
-def swiglu(gate_up, out=None, out_dtype=None, interleave=0):
+def swiglu(gate_up, out=None, out_dtype=None, interleave=0, activation="silu"):
     I = gate_up.shape[1] // 2
     if interleave:
         blocks = gate_up.reshape(gate_up.shape[0], I // interleave, 2, interleave)
         gate_up = torch.cat([blocks[:, :, 0].reshape(-1, I), blocks[:, :, 1].reshape(-1, I)], dim=1)
     g, u = gate_up[:, :I].to(torch.float32), gate_up[:, I:].to(torch.float32)
-    return (g / (1.0 + torch.exp(-g)) * u).to(gate_up.dtype)
+    if activation == "gelu_tanh":
+        return (gelu_tanh(g) * u).to(out_dtype or gate_up.dtype)
+    return (g / (1.0 + torch.exp(-g)) * u).to(out_dtype or gate_up.dtype)
 
 
 def rope_table(n_pos, head_dim, theta, device):
@@ -96,7 +133,167 @@ def qk_norm_rope_store(qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weigh
 
 def linear(x, weight, out_dtype=None, out=None, allow_partials=False):
     y = x.to(torch.float32) @ weight.to(torch.float32).T
+    if out is not None:
+        out.copy_(y)
+        return out
     return y.to(out_dtype or x.dtype)
+
+
+def linear_cuda_cores(x, weight, out_dtype=None):
+    return linear(x, weight, out_dtype=out_dtype)
+
+
+def tensor_core_linear_ok(x, weight):
+    return False
+
+
+def linear_batched(x, weight, out, bias=None, relu2=False):
+    y = torch.einsum("bmk,bnk->bmn", x.to(torch.float32), weight.to(torch.float32))
+    if bias is not None:
+        y = y + bias[:, None, :]
+    if relu2:
+        y = torch.relu(y) ** 2
+    out.copy_(y)
+    return out
+
+
+def linear_grouped(x, weight, out, row_src, tile_group, n_tiles, tile_rows, relu2=False):
+    for tile in range(int(n_tiles[0])):
+        w = weight[int(tile_group[tile])].to(torch.float32)
+        for r in range(tile * tile_rows, (tile + 1) * tile_rows):
+            src = int(row_src[r])
+            if src < 0:
+                continue
+            y = w @ x[src].to(torch.float32)
+            out[r] = torch.relu(y) ** 2 if relu2 else y
+    return out
+
+
+# ---------------------------------------------------------------- mixture of experts
+MOE_TILE_ROWS_SMALL, MOE_TILE_ROWS = 16, 64
+
+
+def moe_route(logits, correction, top, renormalize=False):
+    s = torch.softmax(logits.to(torch.float32), dim=-1)
+    pick = s if correction is None else s + correction
+    chosen = torch.topk(pick, top, dim=-1).indices
+    weight = torch.gather(s, 1, chosen)
+    if renormalize:
+        weight = weight / weight.sum(dim=-1, keepdim=True)
+    return chosen.to(torch.int32), weight
+
+
+def moe_align(chosen, experts, tile_rows):
+    T, top = chosen.shape
+    flat = chosen.reshape(-1).tolist()
+    row_token, row_self, tile_expert = [], [], []
+    pair_row = [-1] * len(flat)
+    for e in range(experts):
+        pairs = [p for p, c in enumerate(flat) if c == e]
+        for p in pairs:
+            pair_row[p] = len(row_token)
+            row_self.append(len(row_token))
+            row_token.append(p // top)
+        pad = -len(pairs) % tile_rows
+        row_token += [-1] * pad
+        row_self += [-1] * pad
+        tile_expert += [e] * ((len(pairs) + pad) // tile_rows)
+    cap = (-(-len(flat) // tile_rows) + experts) * tile_rows
+    n_tiles = len(tile_expert)
+    row_token += [-1] * (cap - len(row_token))
+    row_self += [-1] * (cap - len(row_self))
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32)
+    return i32(row_token), i32(row_self), i32(pair_row), i32(tile_expert + [0] * (cap // tile_rows - n_tiles)), i32([n_tiles])
+
+
+def moe_combine(y, x, chosen, weight, pair_row, experts):
+    T, H = x.shape
+    top = chosen.shape[1]
+    out = torch.zeros((T, H), dtype=torch.float32)
+    for t in range(T):
+        for k in range(top):
+            e = int(chosen[t, k])
+            v = y[int(pair_row[t * top + k])] if e < experts else x[t].to(torch.float32)
+            out[t] += weight[t, k] * v
+    return out.to(x.dtype)
+
+
+# ---------------------------------------------------------------- recurrent mixers
+def _conv_inputs(x, x_bias, state_rows, taps):
+    """The carried inputs (oldest first) followed by this step's inputs of one request."""
+    return torch.cat([state_rows[:taps - 1], x.to(torch.float32) + x_bias], dim=0)
+
+
+def causal_conv(x, x_bias, kernel, bias, state, step):
+    T, C = x.shape
+    taps = kernel.shape[1]
+    u = torch.empty((T, C), dtype=torch.float32)
+    cu, slots = step.cu_q.tolist(), step.state_slots.tolist()
+    for s in range(step.n_seqs):
+        a, b = cu[s], cu[s + 1]
+        seq = _conv_inputs(x[a:b], x_bias, state[slots[s]], taps)
+        for t in range(b - a):
+            u[a + t] = bias + (kernel * seq[t:t + taps].T).sum(dim=1)
+    return u
+
+
+def rglru_scan(u, gates, block_width, r_bias, i_bias, lam, decay_scale, y, y_bias, x, x_bias, state, step):
+    T, C = u.shape
+    taps = state.shape[1]
+    g = gates.reshape(T, C // block_width, 2, block_width)
+    r = torch.sigmoid(g[:, :, 0].reshape(T, C) + r_bias)
+    i = torch.sigmoid(g[:, :, 1].reshape(T, C) + i_bias)
+    log_a = -decay_scale * r * torch.nn.functional.softplus(lam)
+    a = torch.exp(log_a)
+    drive = torch.sqrt(-torch.expm1(2.0 * log_a)) * i * u
+    out = torch.empty((T, C), dtype=torch.float32)
+    cu, slots = step.cu_q.tolist(), step.state_slots.tolist()
+    for s in range(step.n_seqs):
+        lo, hi = cu[s], cu[s + 1]
+        S = state[slots[s], taps - 1].clone()
+        for t in range(lo, hi):
+            S = a[t] * S + drive[t]
+            out[t] = S
+        if taps > 1:
+            seq = _conv_inputs(x[lo:hi], x_bias, state[slots[s]], taps)
+            state[slots[s], :taps - 1] = seq[seq.shape[0] - (taps - 1):]
+        state[slots[s], taps - 1] = S
+    return (out * gelu_tanh(y.to(torch.float32) + y_bias)).to(y.dtype)
+
+
+# ----------------------------------------------------------------- latent attention
+def _rotate_first(v, cos, sin, rot_dims):
+    half = rot_dims // 2
+    a, b = v[..., :half], v[..., half:rot_dims]
+    return torch.cat([a * cos - b * sin, b * cos + a * sin, v[..., rot_dims:]], dim=-1)
+
+
+def latent_prepare(proj, heads, dim, rot_dim, rank, rot_dims, c_weight, eps, cos, sin, positions, q_eff, cache, slots):
+    T = proj.shape[0]
+    D = rank + rot_dim
+    pos = positions.long()
+    c, s = cos[pos], sin[pos]
+    q = proj[:, :heads * (dim + rot_dim)].to(torch.float32).reshape(T, heads, dim + rot_dim)
+    q_eff.view(T, heads, D)[:, :, rank:] = _rotate_first(q[:, :, dim:], c[:, None, :], s[:, None, :], rot_dims).to(q_eff.dtype)
+    if cache is None:
+        return
+    kv = proj[:, heads * (dim + rot_dim):heads * (dim + rot_dim) + D].to(torch.float32)
+    lat = kv[:, :rank]
+    lat = lat * c_weight * (1.0 / torch.sqrt((lat * lat).mean(dim=-1, keepdim=True) + torch.tensor(eps, dtype=torch.float32)))
+    row = torch.cat([lat, _rotate_first(kv[:, rank:], c, s, rot_dims)], dim=-1).to(cache.dtype)
+    page_size = cache.shape[2]
+    for t in range(T):
+        slot = int(slots[t])
+        if slot >= 0:
+            cache[slot // page_size, 0, slot % page_size] = row[t]
+
+
+def latent_attention(q_eff, cache, block_tables, step, heads, rank, page_size, window, scale):
+    T = q_eff.shape[0]
+    D = cache.shape[-1]
+    full = paged_attention(q_eff, cache, cache, block_tables, step.cu_q, step.kv_lens, step.tile_seq, step.tile_q0,
+                           heads, 1, D, page_size, window, scale)
+    return full.view(T, heads, D)[:, :, :rank].reshape(T, heads * rank).contiguous()
 
 
 def attention_tile_rows():

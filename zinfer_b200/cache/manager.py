@@ -1,7 +1,7 @@
 """The cache manager: which pages and which state slot each request holds.
 
 Keys and values live in pages of ``page_size`` tokens.  Caches with the same need
-(kv heads, head size, window) form a *group*: a group has a page pool of its own
+(kv heads, head size, window, with or without values) form a *group*: a group has a page pool of its own
 and one block table per request, valid for every cache of the group.  A request's
 pages are given back when it ends, and, in a group with a window, as soon as the
 window has passed them.  Beside the pages, each request holds one slot for
@@ -34,6 +34,7 @@ class KVNeedKey:
     num_kv_heads: int
     head_dim: int
     window: Optional[int]
+    values: bool = True        # False: pages of keys only
 
 
 @dataclass
@@ -81,7 +82,7 @@ class CacheManager:
         sizes: list[int] = []
         self.group_of: dict[str, tuple[int, int]] = {}   # cache name -> (group, index within the group)
         for name, need in kv_needs.items():
-            key = KVNeedKey(need.num_kv_heads, need.head_dim, need.window)
+            key = KVNeedKey(need.num_kv_heads, need.head_dim, need.window, getattr(need, "values", True))
             if key.window is not None and key.window <= 0:
                 raise ValueError(f"cache {name!r}: window must be positive")
             if key in keys:

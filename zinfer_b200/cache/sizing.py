@@ -2,7 +2,7 @@
 
 One page of a group holds ``page_size`` tokens of keys and of values for every
 cache of the group: ``caches * 2 * kv heads * page_size * head_dim * element size``
-bytes.  Every group gets the same number of pages, so one page id across all groups
+bytes (half of that in a group that keeps keys only).  Every group gets the same number of pages, so one page id across all groups
 costs the sum of those.  The reference sizes one contiguous cache per request by
 the same product over its layers
 (src/model/runtime/optimized_kv_cache/cache.zig:423-456) and prints it with its
@@ -13,18 +13,19 @@ from __future__ import annotations
 from typing import Optional
 
 
-def group_shapes(kv_needs: dict) -> list[tuple[int, int, int]]:
-    """(caches, kv heads, head size) per group, grouping equal needs like the manager does."""
+def group_shapes(kv_needs: dict) -> list[tuple[int, int, int, int]]:
+    """(caches, kv heads, head size, planes) per group, grouping equal needs like the manager does;
+    planes is 2 (keys and values) or 1 (keys only)."""
     groups: dict[tuple, int] = {}
     for need in kv_needs.values():
-        key = (need.num_kv_heads, need.head_dim, need.window)
+        key = (need.num_kv_heads, need.head_dim, need.window, 2 if getattr(need, "values", True) else 1)
         groups[key] = groups.get(key, 0) + 1
-    return [(n, key[0], key[1]) for key, n in groups.items()]
+    return [(n, key[0], key[1], key[3]) for key, n in groups.items()]
 
 
 def bytes_per_page(kv_needs: dict, page_size: int, element_size: int) -> int:
     """Bytes that one more page in every group costs."""
-    return sum(n * 2 * heads * page_size * d * element_size for n, heads, d in group_shapes(kv_needs))
+    return sum(n * planes * heads * page_size * d * element_size for n, heads, d, planes in group_shapes(kv_needs))
 
 
 def bytes_per_token(kv_needs: dict, element_size: int) -> int:

@@ -1,8 +1,8 @@
 """Device memory behind the cache manager's ids.
 
 For each group one tensor ``[caches, 2, pages, kv heads, page_size, head_dim]``
-(keys at index 0, values at index 1) in the run's dtype: a page id is valid for
-every cache of the group.  For each state cache one tensor
+(keys at index 0, values at index 1; ``[caches, 1, ...]`` for a group that keeps keys
+only) in the run's dtype: a page id is valid for every cache of the group.  For each state cache one tensor
 ``[request slots + 1, *shape]``, zeroed for a slot when a request takes it.  The last
 slot belongs to no request: the rows that pad a captured decode batch name it, so a
 mixer that updates ``state[state_slots]`` with device operations alone harms nobody.
@@ -10,6 +10,8 @@ mixer that updates ``state[state_slots]`` with device operations alone harms nob
 from __future__ import annotations
 
 from dataclasses import dataclass
+from typing import Optional
+
 import torch
 
 from .manager import CacheManager
@@ -20,7 +22,7 @@ class KVCacheView:
     """What an attention-like mixer gets for one run of its layer."""
 
     k: torch.Tensor          # [pages, kv heads, page_size, head_dim]
-    v: torch.Tensor
+    v: Optional[torch.Tensor]   # None in a group that keeps keys only
     group: int               # index into StepContext.kv_groups
     page_size: int
     writes: bool             # False: this run only reads a cache another run wrote
@@ -40,7 +42,8 @@ class CacheStorage:
         self.manager = manager
         self.kv: list[torch.Tensor] = []
         for g in manager.groups:
-            shape = (len(g.caches), 2, g.pool.num_pages, g.key.num_kv_heads, manager.page_size, g.key.head_dim)
+            shape = (len(g.caches), 2 if g.key.values else 1, g.pool.num_pages, g.key.num_kv_heads, manager.page_size,
+                     g.key.head_dim)
             self.kv.append(torch.zeros(shape, dtype=dtype, device=device))
         self.state: dict[str, torch.Tensor] = {
             name: torch.zeros((manager.max_requests + 1, *need.shape), dtype=need.dtype, device=device)
@@ -50,7 +53,8 @@ class CacheStorage:
     def kv_view(self, cache_name: str, writes: bool) -> KVCacheView:
         gi, ci = self.manager.group_of[cache_name]
         t = self.kv[gi]
-        return KVCacheView(k=t[ci, 0], v=t[ci, 1], group=gi, page_size=self.manager.page_size, writes=writes)
+        return KVCacheView(k=t[ci, 0], v=t[ci, 1] if t.shape[1] > 1 else None, group=gi,
+                           page_size=self.manager.page_size, writes=writes)
 
     def state_view(self, cache_name: str, writes: bool = True) -> StateView:
         return StateView(self.state[cache_name], writes)
@@ -64,7 +68,8 @@ class CacheStorage:
         cache of the group (debugging: what a freed page held must never reach a result)."""
         idx = torch.as_tensor(list(pages), dtype=torch.long, device=self.kv[group].device)
         self.kv[group][:, 0].index_fill_(1, idx, value)
-        self.kv[group][:, 1].index_fill_(1, idx, -value)
+        if self.kv[group].shape[1] > 1:
+            self.kv[group][:, 1].index_fill_(1, idx, -value)
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.kv) + \

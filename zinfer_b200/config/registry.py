@@ -1,8 +1,8 @@
 """The one registry from an architecture's name to its model.
 
 An entry holds the typed configuration class and the function that turns a
-configuration into a :class:`ModelSpec`.  Lookup is by ``architectures[0]`` of
-config.json, with ``model_type`` as a second key; the reference detects the family
+configuration into a :class:`ModelSpec`.  Lookup is by ``architectures[0]`` (or the
+single string ``architecture``) of config.json, with ``model_type`` as a second key; the reference detects the family
 by ``model_type`` alone (src/model/runtime/decoder_family.zig:267-281) and keeps
 its entries in a table of constants and functions
 (src/model/runtime/decoder_registry.zig:7-21).
@@ -53,10 +53,12 @@ def registered() -> list[str]:
 def family_for(config: dict) -> Family:
     """Family of a raw config.json dictionary."""
     keys = list(config.get("architectures") or [])[:1]
+    if isinstance(config.get("architecture"), str):     # some designs name themselves with a single string
+        keys.append(config["architecture"])
     if "model_type" in config:
         keys.append(config["model_type"])
     if not keys:
-        raise UnknownArchitecture("config.json names neither `architectures` nor `model_type`")
+        raise UnknownArchitecture("config.json names neither `architectures`, `architecture` nor `model_type`")
     for k in keys:
         if k in _FAMILIES:
             return _FAMILIES[k]

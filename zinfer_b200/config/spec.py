@@ -46,11 +46,13 @@ class ScheduleEntry:
     ``layer`` indexes ``ModelSpec.layers``.  ``cache`` names the cache this run
     uses; entries with the same ``cache`` share it, the first of them in schedule
     order writes it and the later ones only read it.  ``None`` gives the entry a
-    cache of its own.
+    cache of its own.  ``pre_add`` names a row of one of the model's ``tables``
+    (name, row): that vector is added to the residual stream right before this run.
     """
 
     layer: int
     cache: Optional[str] = None
+    pre_add: Optional[tuple[str, int]] = None
 
 
 @dataclass(frozen=True)
@@ -65,13 +67,21 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     eos_token_ids: tuple[int, ...] = ()
+    # tensors of the model itself (not of a layer), by name: tables of vectors [rows, hidden_size]
+    # that schedule entries add to the residual stream
+    tables: tuple[tuple[str, tuple[int, ...]], ...] = ()
 
     def validate(self) -> None:
         if not self.layers:
             raise ValueError("ModelSpec has no layers")
+        shapes = dict(self.tables)
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule[{i}] names layer {e.layer}, but there are {len(self.layers)} layers")
+            if e.pre_add is not None:
+                name, row = e.pre_add
+                if name not in shapes or not 0 <= row < shapes[name][0] or shapes[name][1:] != (self.hidden_size,):
+                    raise ValueError(f"schedule[{i}] adds row {row} of {name!r}, which is no row of a table of the model")
 
 
 def default_schedule(n_layers: int) -> tuple[ScheduleEntry, ...]:

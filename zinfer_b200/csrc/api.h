@@ -16,7 +16,19 @@ int zi_embed_gather(float* h, const void* table, int table_dtype, const int* ids
 int zi_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* delta_partials, int splits,
                    long long split_stride, const float* w, float eps, void* out, int out_dtype, const int* rows,
                    int n_rows, int H, cudaStream_t stream);
+int zi_add_rmsnorm_scaled(float* h, const void* delta, int delta_dtype, const float* delta_partials, int splits,
+                          long long split_stride, float delta_scale, const float* bias, const float* w, float eps,
+                          void* out, int out_dtype, const int* rows, int n_rows, int H, cudaStream_t stream);
 int zi_residual_add(float* h, const void* delta, int delta_dtype, long long n, cudaStream_t stream);
+int zi_residual_add_scaled(float* h, const void* delta, int delta_dtype, float delta_scale, long long n,
+                           cudaStream_t stream);
+int zi_scale_f32(float* x, long long n, float s, cudaStream_t stream);
+int zi_sigmoid_gate(void* out, int ldo, const void* x, int ldx, const void* g, int ldg, int dtype, int T, int width,
+                    cudaStream_t stream);
+// act: 0 silu, 1 the tanh form of gelu
+int zi_gated_act(void* out, const void* gu, int dtype, int T, int I, int interleave, int act, cudaStream_t stream);
+int zi_gated_act_partials(void* out, int dtype, const float* partials, int splits, long long split_stride, int T, int I,
+                          int interleave, int act, cudaStream_t stream);
 int zi_residual_add_partials(float* h, const float* partials, int splits, long long split_stride, long long n,
                              cudaStream_t stream);
 int zi_patch_tokens(int* ids, const int* prev, const int* dst, const int* src, int n, cudaStream_t stream);
@@ -38,6 +50,23 @@ int zi_qk_norm_rope_store(const void* src, int dtype, int T, int src_stride, con
 int zi_gemm_simt(void* out, int out_dtype, const void* x, int x_dtype, const void* w, int w_dtype, int M, int N,
                  int K, int ldx, int ldw, int ldo, cudaStream_t stream);
 
+// Batched (`batch` products sx/sw/so/sb elements apart) and grouped (per-tile weight group, gathered rows, sizes on
+// the device) forms of the CUDA-core product; epilogue 0: none, 1: square of relu; tile_rows 16 or 64.
+int zi_gemm_simt_general(void* out, int out_dtype, const void* x, int x_dtype, const void* w, int w_dtype, int M, int N,
+                         int K, int ldx, int ldw, int ldo, int batch, long long sx, long long sw, long long so,
+                         const float* bias, long long sb, const int* row_src, const int* tile_group,
+                         const int* n_tiles_dev, long long group_stride, int epilogue, int tile_rows,
+                         cudaStream_t stream);
+
+// Recurrent mixers: state [slots][taps][C] float32 (taps-1 carried inputs of the convolution, then S).
+int zi_causal_conv(float* u, const void* x, int ldx, int dtype, const float* xb, const float* kern, const float* cb,
+                   const float* state, int C, int taps, const int* cu_q, const int* state_slots, int n_seqs, int T,
+                   cudaStream_t stream);
+int zi_rglru_scan(void* out, int ldo, const float* u, const float* gates, int block_width, const float* rb,
+                  const float* ib, const float* lam, float decay_scale, const void* y, int ldy, const float* yb,
+                  const void* x, int ldx, const float* xb, int dtype, float* state, int C, int taps, const int* cu_q,
+                  const int* state_slots, int n_seqs, cudaStream_t stream);
+
 int zi_gemm_tcgen05_supported(const void* x, const void* w, int K, int ldx, int ldw);
 long long zi_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* plan);
 int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K, int ldx, int ldw,
@@ -51,6 +80,24 @@ int zi_paged_attention(void* out, int out_stride, const void* q, int q_stride, i
                        const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
                        const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
                        int d, int page_size, int window, float scale, cudaStream_t stream);
+
+// The same with dv <= d value columns read from rows of v_row elements (values may lie in the key rows).
+int zi_paged_attention_v(void* out, int out_stride, const void* q, int q_stride, int dtype, const void* kcache,
+                         const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
+                         const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
+                         int d, int dv, int v_row, int page_size, int window, float scale, cudaStream_t stream);
+// Latent attention: the cached row [normed latent | rotated key part] and the rotated query part of a token.
+int zi_latent_prepare(const void* src, int ld, int dtype, int T, int heads, int dim, int rd, int rank, int rot_dims,
+                      const float* cw, float eps, const float* cos_t, const float* sin_t, int n_table_pos,
+                      const int* positions, void* q_eff, void* cache, const int* slots, int write_cache,
+                      cudaStream_t stream);
+// Mixture of experts: choice and weights per token, the pairs laid out by expert, the weighted sum.
+int zi_moe_route(int* chosen, float* weight, const float* logits, const float* correction, int T, int NR, int top,
+                 int renormalize, cudaStream_t stream);
+int zi_moe_align(const int* chosen, int P, int top, int E, int tile_rows, int* row_token, int* row_self, int* pair_row,
+                 int* tile_expert, int* n_tiles, cudaStream_t stream);
+int zi_moe_combine(void* out, const float* y, const void* x, int dtype, const int* chosen, const float* weight,
+                   const int* pair_row, int T, int top, int E, int H, cudaStream_t stream);
 
 int zi_attention_prefill_tile_rows();
 int zi_attention_mma_supported(int nq, int nkv, int d, int decode);

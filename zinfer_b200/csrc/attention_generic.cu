@@ -13,23 +13,26 @@
 #include "common.cuh"
 
 namespace {
-constexpr int BQ = 16, BK = 32, THREADS = 128, ROWS_PER_WARP = BQ / (THREADS / 32), MAXJ = 8;
+constexpr int BQ = 16, BK = 32, THREADS = 128, ROWS_PER_WARP = BQ / (THREADS / 32);
 
-template <typename T>
+// Values may be narrower than keys and may lie in the key rows themselves (a latent cache whose row
+// serves as key and, in its first dv columns, as value): dv value columns are read from rows of
+// v_row elements in `vcache`; the output has dv columns per head.  MAXJ * 32 bounds dv.
+template <typename T, int MAXJ>
 __global__ void __launch_bounds__(THREADS)
 paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ q, int q_stride,
                        const T* __restrict__ kcache, const T* __restrict__ vcache,
                        const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_q,
                        const int* __restrict__ kv_lens, const int* __restrict__ tile_seq,
                        const int* __restrict__ tile_q0, int nq, int nkv, int d, int page_size, int window,
-                       float scale) {
+                       float scale, int dv, int v_row) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float smem[];
   float* Qs = smem;                   // [BQ][d]
   float* Ks = Qs + BQ * d;            // [BK][d+1]
-  float* Vs = Ks + BK * (d + 1);      // [BK][d]
-  float* Ss = Vs + BK * d;            // [BQ][BK]
+  float* Vs = Ks + BK * (d + 1);      // [BK][dv]
+  float* Ss = Vs + BK * dv;           // [BQ][BK]
 
   const int seq = tile_seq[blockIdx.x], q0 = tile_q0[blockIdx.x];
   const int h = blockIdx.y, kvh = h / (nq / nkv);
@@ -66,13 +69,13 @@ paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict_
       if (j >= kv_begin && j < kv_end) {
         const int page = bt[j / page_size];
         if (page >= 0) {
-          const size_t off = (((size_t)page * nkv + kvh) * page_size + (j % page_size)) * d + c;
-          kval = to_f32(kcache[off]);
-          vval = to_f32(vcache[off]);
+          const size_t r = ((size_t)page * nkv + kvh) * page_size + (j % page_size);
+          kval = to_f32(kcache[r * d + c]);
+          if (c < dv) vval = to_f32(vcache[r * v_row + c]);
         }
       }
       Ks[kk * (d + 1) + c] = kval;
-      Vs[kk * d + c] = vval;
+      if (c < dv) Vs[kk * dv + c] = vval;
     }
     __syncthreads();
 
@@ -112,7 +115,7 @@ paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict_
 #pragma unroll
         for (int j = 0; j < MAXJ; ++j) {
           const int c = lane + 32 * j;
-          if (c < d) acc[i][j] = fmaf(p, Vs[kk * d + c], acc[i][j]);
+          if (c < dv) acc[i][j] = fmaf(p, Vs[kk * dv + c], acc[i][j]);
         }
       }
     }
@@ -122,11 +125,11 @@ paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict_
     const int r = warp * ROWS_PER_WARP + i;
     if (r >= nqv) continue;
     const float inv = 1.0f / l[i];
-    T* o = out + (size_t)(tok0 + q0 + r) * out_stride + (size_t)h * d;
+    T* o = out + (size_t)(tok0 + q0 + r) * out_stride + (size_t)h * dv;
 #pragma unroll
     for (int j = 0; j < MAXJ; ++j) {
       const int c = lane + 32 * j;
-      if (c < d) o[c] = from_f32<T>(acc[i][j] * inv);
+      if (c < dv) o[c] = from_f32<T>(acc[i][j] * inv);
     }
   }
 }
@@ -139,22 +142,39 @@ extern "C" int zi_paged_attention(void* out, int out_stride, const void* q, int 
                                   const int* cu_q, const int* kv_lens, const int* tile_seq, const int* tile_q0,
                                   int n_tiles, int nq, int nkv, int d, int page_size, int window, float scale,
                                   cudaStream_t stream) {
+  return zi_paged_attention_v(out, out_stride, q, q_stride, dtype, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
+                              tile_seq, tile_q0, n_tiles, nq, nkv, d, d, d, page_size, window, scale, stream);
+}
+
+extern "C" int zi_paged_attention_v(void* out, int out_stride, const void* q, int q_stride, int dtype,
+                                    const void* kcache, const void* vcache, const int* block_tables, int bt_stride,
+                                    const int* cu_q, const int* kv_lens, const int* tile_seq, const int* tile_q0,
+                                    int n_tiles, int nq, int nkv, int d, int dv, int v_row, int page_size, int window,
+                                    float scale, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
-  if (d <= 0 || d > 32 * MAXJ) return zi_refuse("paged_attention: head_dim %d is outside 1..%d", d, 32 * MAXJ);
+  constexpr int WIDE = 20;   // value columns up to 640 (latent caches); 8 serves every ordinary head size
+  if (d <= 0 || d > 32 * WIDE) return zi_refuse("paged_attention: head_dim %d is outside 1..%d", d, 32 * WIDE);
+  if (dv <= 0 || dv > d || v_row < dv) return zi_refuse("paged_attention: %d value columns of rows of %d, keys of %d", dv, v_row, d);
   if (nkv <= 0 || nq % nkv) return zi_refuse("paged_attention: %d query heads do not divide into %d kv heads", nq, nkv);
   if (page_size <= 0) return zi_refuse("paged_attention: page_size %d", page_size);
-  const size_t smem = (size_t)(BQ * d + BK * (d + 1) + BK * d + BQ * BK) * sizeof(float);
+  const size_t smem = (size_t)(BQ * d + BK * (d + 1) + BK * dv + BQ * BK) * sizeof(float);
   dim3 grid(n_tiles, nq);
+#define ZI_LAUNCH_ATTN(J)                                                                                          \
+  do {                                                                                                             \
+    auto kern = paged_attention_kernel<TT, J>;                                                                     \
+    if (smem > 48 * 1024) {                                                                                        \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
+      if (e != cudaSuccess) return zi_refuse("paged_attention: cannot get %zu bytes of shared memory", smem);      \
+    }                                                                                                              \
+    zi_launch(kern, dim3(grid), dim3(THREADS), smem, stream, (TT*)out, out_stride, (const TT*)q, q_stride,         \
+              (const TT*)kcache, (const TT*)vcache, block_tables, bt_stride, cu_q, kv_lens, tile_seq, tile_q0, nq, \
+              nkv, d, page_size, window, scale, dv, v_row);                                                        \
+  } while (0)
   ZI_DISPATCH_DTYPE(dtype, TT, {
-    auto kern = paged_attention_kernel<TT>;
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return zi_refuse("paged_attention: cannot get %zu bytes of shared memory", smem);
-    }
-    zi_launch(kern, dim3(grid), dim3(THREADS), smem, stream, (TT*)out, out_stride, (const TT*)q, q_stride, (const TT*)kcache,
-                                          (const TT*)vcache, block_tables, bt_stride, cu_q, kv_lens, tile_seq,
-                                          tile_q0, nq, nkv, d, page_size, window, scale);
+    if (dv <= 256) ZI_LAUNCH_ATTN(8);
+    else ZI_LAUNCH_ATTN(WIDE);
   });
+#undef ZI_LAUNCH_ATTN
   return zi_check_launch("paged_attention");
 }
 

@@ -8,6 +8,12 @@
 #define ZI_F32 0
 #define ZI_BF16 1
 
+// activation tags of the gated feed-forward kernels
+#define ZI_EPI_NONE 0
+#define ZI_EPI_RELU2 1
+#define ZI_ACT_SILU 0
+#define ZI_ACT_GELU_TANH 1
+
 // Entry points return 0, a cudaError_t (> 0), or ZI_REFUSED (< 0) with the reason
 // in zi_last_error().
 #define ZI_REFUSED (-1)
@@ -25,6 +31,12 @@ __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162flo
 template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// the tanh form of gelu: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), in 32-bit with the exact tanhf
+__device__ __forceinline__ float gelu_tanh_f32(float z) {
+  const float inner = 0.7978845608028654f * fmaf(0.044715f * z * z, z, z);
+  return 0.5f * z * (1.0f + tanhf(inner));
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

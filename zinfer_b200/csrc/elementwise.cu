@@ -35,11 +35,14 @@ extern "C" int zi_embed_gather(float* h, const void* table, int table_dtype, con
 // With `rows` (a gather of picked rows, possibly with repeats) h itself is not modified.
 // One block per row; the sum of squares is taken in a fixed order.
 // The update may also come as split-K partial sums: dpart[z][row][i], z < splits, added in order.
+// The update is multiplied by `dscale` as it is added (a residual multiplier; 1 changes no bit), and
+// `bias` [H], when given, is added to every row as well (a vector a model adds between two layers).
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta,
                                    const float* __restrict__ dpart, int splits, size_t zstride,
                                    const float* __restrict__ w, float eps, TO* __restrict__ out,
-                                   const int* __restrict__ rows, int H) {
+                                   const int* __restrict__ rows, int H, float dscale,
+                                   const float* __restrict__ bias) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float scratch[33];
@@ -52,20 +55,26 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float d = 0.f;
       for (int z = 0; z < splits; ++z) d += dr[z * zstride + i];
-      const float v = hr[i] + d;
+      float v = fmaf(dscale, d, hr[i]);
+      if (bias) v += bias[i];
       if (!rows) hr[i] = v;
       ss += v * v;
     }
   } else if (delta) {
     const TD* dr = delta + (size_t)row * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
-      float v = hr[i] + to_f32(dr[i]);
+      float v = fmaf(dscale, to_f32(dr[i]), hr[i]);
+      if (bias) v += bias[i];
       if (!rows) hr[i] = v;
       ss += v * v;
     }
   } else {
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float v = hr[i];
+      if (bias) {
+        v += bias[i];
+        if (!rows) hr[i] = v;
+      }
       ss += v * v;
     }
   }
@@ -81,10 +90,11 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
       if (dpart) {
         float d = 0.f;
         for (int z = 0; z < splits; ++z) d += dpart[z * zstride + (size_t)row * H + i];
-        v += d;
+        v = fmaf(dscale, d, v);
       } else if (delta) {
-        v += to_f32(delta[(size_t)row * H + i]);
+        v = fmaf(dscale, to_f32(delta[(size_t)row * H + i]), v);
       }
+      if (bias) v += bias[i];
       o[i] = from_f32<TO>(v * w[i] * inv);
     }
   }
@@ -118,7 +128,8 @@ template <typename TD, typename TO, int VPT, bool PART>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta,
                                        const float* __restrict__ dpart, int splits, size_t zstride,
                                        const float* __restrict__ w, float eps, TO* __restrict__ out,
-                                       const int* __restrict__ rows, int H, int n_rows) {
+                                       const int* __restrict__ rows, int H, int n_rows, float dscale,
+                                       const float* __restrict__ bias) {
   pdl_launch_dependents();
   __shared__ float scratch[33];
   const int nvec = H >> 2;
@@ -170,13 +181,17 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
           const float4 p = Vec4<float>::load(base + (size_t)z * zstride);
           d.x += p.x; d.y += p.y; d.z += p.z; d.w += p.w;
         }
-        a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
-        if (!rows) Vec4<float>::store(hr + 4 * idx, a);   // picked rows leave h as it is (a row may be picked twice)
+        a.x = fmaf(dscale, d.x, a.x); a.y = fmaf(dscale, d.y, a.y); a.z = fmaf(dscale, d.z, a.z); a.w = fmaf(dscale, d.w, a.w);
       } else if (delta) {
         const float4 d = Vec4<TD>::load(delta + (size_t)row * H + 4 * idx);
-        a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
-        if (!rows) Vec4<float>::store(hr + 4 * idx, a);
+        a.x = fmaf(dscale, d.x, a.x); a.y = fmaf(dscale, d.y, a.y); a.z = fmaf(dscale, d.z, a.z); a.w = fmaf(dscale, d.w, a.w);
       }
+      if (bias) {
+        const float4 b = Vec4<float>::load(bias + 4 * idx);
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+      }
+      // picked rows leave h as it is (a row may be picked twice)
+      if (!rows && (PART || delta || bias)) Vec4<float>::store(hr + 4 * idx, a);
       v[i] = a;
       ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
     }
@@ -210,8 +225,8 @@ static int sm_count_of_current_device() {
 template <typename TD, typename TO>
 static int launch_add_rmsnorm(float* h, const void* delta, const float* dpart, int splits, size_t zstride,
                               const float* w, float eps, void* out, const int* rows, int n_rows, int H,
-                              cudaStream_t stream) {
-  const bool aligned = H % 4 == 0 && ((uintptr_t)h % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
+                              float dscale, const float* bias, cudaStream_t stream) {
+  const bool aligned = H % 4 == 0 && ((uintptr_t)h % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)bias % 16 == 0) &&
                        ((uintptr_t)out % 16 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)dpart % 16 == 0) &&
                        zstride % 4 == 0;
   const int nvec = H / 4;
@@ -231,7 +246,7 @@ static int launch_add_rmsnorm(float* h, const void* delta, const float* dpart, i
       slot = 1;                                                                                                    \
     const int resident = sm_count_of_current_device() * slot;                                                      \
     zi_launch(kern, dim3(n_rows < resident ? n_rows : resident), dim3(threads), 0, stream, h, (const TD*)delta, dpart, \
-              splits, zstride, w, eps, (TO*)out, rows, H, n_rows);                                                 \
+              splits, zstride, w, eps, (TO*)out, rows, H, n_rows, dscale, bias);                                   \
   } while (0)
 #define ZI_LAUNCH_PART(V)            \
   do {                               \
@@ -247,7 +262,7 @@ static int launch_add_rmsnorm(float* h, const void* delta, const float* dpart, i
   } else {
     const int t2 = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     zi_launch(add_rmsnorm_kernel<TD, TO>, dim3(n_rows), dim3(t2), 0, stream, h, (const TD*)delta, dpart, splits, zstride, w, eps, (TO*)out,
-                                                          rows, H);
+                                                          rows, H, dscale, bias);
   }
   return zi_check_launch("add_rmsnorm");
 }
@@ -255,37 +270,55 @@ static int launch_add_rmsnorm(float* h, const void* delta, const float* dpart, i
 extern "C" int zi_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* delta_partials, int splits,
                               long long split_stride, const float* w, float eps, void* out, int out_dtype,
                               const int* rows, int n_rows, int H, cudaStream_t stream) {
+  return zi_add_rmsnorm_scaled(h, delta, delta_dtype, delta_partials, splits, split_stride, 1.0f, nullptr, w, eps, out,
+                               out_dtype, rows, n_rows, H, stream);
+}
+
+extern "C" int zi_add_rmsnorm_scaled(float* h, const void* delta, int delta_dtype, const float* delta_partials,
+                                     int splits, long long split_stride, float delta_scale, const float* bias,
+                                     const float* w, float eps, void* out, int out_dtype, const int* rows, int n_rows,
+                                     int H, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (delta && delta_partials) return zi_refuse("add_rmsnorm: give the update either whole or as partial sums");
   ZI_DISPATCH_DTYPE(delta_dtype, TD, ZI_DISPATCH_DTYPE(out_dtype, TO, {
                       return launch_add_rmsnorm<TD, TO>(h, delta, delta_partials, splits, (size_t)split_stride, w, eps,
-                                                        out, rows, n_rows, H, stream);
+                                                        out, rows, n_rows, H, delta_scale, bias, stream);
                     }));
   return 0;
 }
 
 // Plain add of the last pending update into the residual stream (rows optional).
 template <typename TD>
-__global__ void residual_add_kernel(float* __restrict__ h, const TD* __restrict__ delta, size_t n) {
+__global__ void residual_add_kernel(float* __restrict__ h, const TD* __restrict__ delta, size_t n, float dscale) {
   pdl_launch_dependents();
   pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) h[i] += to_f32(delta[i]);
+  if (i < n) h[i] = fmaf(dscale, to_f32(delta[i]), h[i]);
 }
 
 extern "C" int zi_residual_add(float* h, const void* delta, int delta_dtype, long long n, cudaStream_t stream) {
+  return zi_residual_add_scaled(h, delta, delta_dtype, 1.0f, n, stream);
+}
+
+extern "C" int zi_residual_add_scaled(float* h, const void* delta, int delta_dtype, float delta_scale, long long n,
+                                      cudaStream_t stream) {
   if (n <= 0) return 0;
   const int threads = 256;
   const unsigned blocks = (unsigned)((n + threads - 1) / threads);
   ZI_DISPATCH_DTYPE(delta_dtype, TD,
-                    zi_launch(residual_add_kernel<TD>, dim3(blocks), dim3(threads), 0, stream, h, (const TD*)delta, (size_t)n));
+                    zi_launch(residual_add_kernel<TD>, dim3(blocks), dim3(threads), 0, stream, h, (const TD*)delta, (size_t)n, delta_scale));
   return zi_check_launch("residual_add");
 }
 
 // --------------------------------------------------------------------------- SwiGLU
 // gu is [T, 2I].  interleave == 0: gate in the first I columns, up in the last I.
 // interleave == 64: blocks of 128 columns hold 64 gate then the 64 up values of the same
-// features.  out[t,i] = silu(g) * u.
+// features.  out[t,i] = act(g) * u, act = silu (ZI_ACT_SILU) or the tanh form of gelu (ZI_ACT_GELU_TANH).
+template <int ACT>
+__device__ __forceinline__ float gated(float g, float u) {
+  if (ACT == ZI_ACT_GELU_TANH) return gelu_tanh_f32(g) * u;
+  return g / (1.0f + expf(-g)) * u;
+}
 __device__ __forceinline__ void gate_up_columns(int i, int I, int interleave, int& gcol, int& ucol) {
   if (interleave) {
     gcol = (i / interleave) * 2 * interleave + (i % interleave);
@@ -296,7 +329,7 @@ __device__ __forceinline__ void gate_up_columns(int i, int I, int interleave, in
   }
 }
 
-template <typename T>
+template <typename T, int ACT>
 __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int I, size_t total, int interleave) {
   pdl_launch_dependents();
   pdl_wait();
@@ -308,11 +341,11 @@ __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int
   gate_up_columns(i, I, interleave, gc, uc);
   const float g = to_f32(gu[t * 2 * I + gc]);
   const float u = to_f32(gu[t * 2 * I + uc]);
-  out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+  out[idx] = from_f32<T>(gated<ACT>(g, u));
 }
 
 // gate and up given as split-K partial sums part[z][t][2I]; four elements per thread.
-template <typename T>
+template <typename T, int ACT>
 __global__ void swiglu_partials_kernel(T* __restrict__ out, const float* __restrict__ part, int splits, size_t zstride,
                                        int I, size_t total_vec, int interleave) {
   pdl_launch_dependents();
@@ -342,12 +375,12 @@ __global__ void swiglu_partials_kernel(T* __restrict__ out, const float* __restr
       }
     }
   }
-  Vec4<T>::store(out + t * I + i, make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y,
-                                              g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w));
+  Vec4<T>::store(out + t * I + i, make_float4(gated<ACT>(g.x, u.x), gated<ACT>(g.y, u.y), gated<ACT>(g.z, u.z),
+                                              gated<ACT>(g.w, u.w)));
 }
 
 // Eight elements per thread (16-byte loads of bfloat16, two of float); needs I % 8 == 0.
-template <typename T>
+template <typename T, int ACT>
 __global__ void swiglu_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, int I, size_t total_vec,
                                   int interleave) {
   pdl_launch_dependents();
@@ -365,24 +398,41 @@ __global__ void swiglu_vec_kernel(T* __restrict__ out, const T* __restrict__ gu,
 #pragma unroll
   for (int k = 0; k < 8; k += 4) {
     const float4 gv = Vec4<T>::load(g + k), uv = Vec4<T>::load(u + k);
-    Vec4<T>::store(o + k, make_float4(gv.x / (1.0f + expf(-gv.x)) * uv.x, gv.y / (1.0f + expf(-gv.y)) * uv.y,
-                                      gv.z / (1.0f + expf(-gv.z)) * uv.z, gv.w / (1.0f + expf(-gv.w)) * uv.w));
+    Vec4<T>::store(o + k, make_float4(gated<ACT>(gv.x, uv.x), gated<ACT>(gv.y, uv.y), gated<ACT>(gv.z, uv.z),
+                                      gated<ACT>(gv.w, uv.w)));
   }
 }
 
+#define ZI_DISPATCH_ACT(act, ACT, ...)                                              \
+  do {                                                                             \
+    if ((act) == ZI_ACT_SILU) { constexpr int ACT = ZI_ACT_SILU; __VA_ARGS__; }     \
+    else if ((act) == ZI_ACT_GELU_TANH) { constexpr int ACT = ZI_ACT_GELU_TANH; __VA_ARGS__; } \
+    else return zi_refuse("unknown activation tag %d", (int)(act));                \
+  } while (0)
+
 extern "C" int zi_swiglu_partials(void* out, int dtype, const float* partials, int splits, long long split_stride,
                                   int T, int I, int interleave, cudaStream_t stream) {
+  return zi_gated_act_partials(out, dtype, partials, splits, split_stride, T, I, interleave, ZI_ACT_SILU, stream);
+}
+
+extern "C" int zi_swiglu(void* out, const void* gu, int dtype, int T, int I, int interleave, cudaStream_t stream) {
+  return zi_gated_act(out, gu, dtype, T, I, interleave, ZI_ACT_SILU, stream);
+}
+
+extern "C" int zi_gated_act_partials(void* out, int dtype, const float* partials, int splits, long long split_stride,
+                                     int T, int I, int interleave, int act, cudaStream_t stream) {
   const size_t total = (size_t)T * I;
   if (total == 0) return 0;
   if (I % 4 || (uintptr_t)partials % 16 || (uintptr_t)out % 8 || split_stride % 4)
     return zi_refuse("swiglu_partials: needs I %% 4 == 0 and aligned buffers");
   const size_t total_vec = total / 4;
-  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(swiglu_partials_kernel<TT>, dim3((unsigned)((total_vec + 255) / 256)), dim3(256), 0, stream, 
-                                   (TT*)out, partials, splits, (size_t)split_stride, I, total_vec, interleave));
+  ZI_DISPATCH_ACT(act, ACT, ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(swiglu_partials_kernel<TT, ACT>, dim3((unsigned)((total_vec + 255) / 256)), dim3(256), 0, stream,
+                                   (TT*)out, partials, splits, (size_t)split_stride, I, total_vec, interleave)));
   return zi_check_launch("swiglu_partials");
 }
 
-extern "C" int zi_swiglu(void* out, const void* gu, int dtype, int T, int I, int interleave, cudaStream_t stream) {
+extern "C" int zi_gated_act(void* out, const void* gu, int dtype, int T, int I, int interleave, int act,
+                            cudaStream_t stream) {
   if (interleave && (interleave % 8 || I % interleave)) return zi_refuse("swiglu: interleave %d does not fit I = %d", interleave, I);
   const size_t total = (size_t)T * I;
   if (total == 0) return 0;
@@ -390,12 +440,12 @@ extern "C" int zi_swiglu(void* out, const void* gu, int dtype, int T, int I, int
   if (I % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gu % 16 == 0) {
     const size_t total_vec = total / 8;
     const unsigned blocks = (unsigned)((total_vec + threads - 1) / threads);
-    ZI_DISPATCH_DTYPE(dtype, TT,
-                      zi_launch(swiglu_vec_kernel<TT>, dim3(blocks), dim3(threads), 0, stream, (TT*)out, (const TT*)gu, I, total_vec, interleave));
+    ZI_DISPATCH_ACT(act, ACT, ZI_DISPATCH_DTYPE(dtype, TT,
+                      zi_launch(swiglu_vec_kernel<TT, ACT>, dim3(blocks), dim3(threads), 0, stream, (TT*)out, (const TT*)gu, I, total_vec, interleave)));
     return zi_check_launch("swiglu");
   }
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
-  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(swiglu_kernel<TT>, dim3(blocks), dim3(threads), 0, stream, (TT*)out, (const TT*)gu, I, total, interleave));
+  ZI_DISPATCH_ACT(act, ACT, ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(swiglu_kernel<TT, ACT>, dim3(blocks), dim3(threads), 0, stream, (TT*)out, (const TT*)gu, I, total, interleave)));
   return zi_check_launch("swiglu");
 }
 
@@ -688,3 +738,41 @@ extern "C" int zi_patch_tokens(int* ids, const int* prev, const int* dst, const 
 }
 
 ZI_TRACE_SETTER(elementwise)
+
+// ------------------------------------------------------------------- small elementwise pieces
+// x[i] *= s over a 32-bit array (a model's multiplier on its logits).
+__global__ void scale_f32_kernel(float* __restrict__ x, size_t n, float s) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] *= s;
+}
+
+extern "C" int zi_scale_f32(float* x, long long n, float s, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  zi_launch(scale_f32_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, (size_t)n, s);
+  return zi_check_launch("scale_f32");
+}
+
+// out[t, c] = x[t, c] * sigmoid(g[t, c]) for rows of `width` values with free row pitches (an output gate).
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ out, int ldo, const T* __restrict__ x, int ldx, const T* __restrict__ g,
+                                    int ldg, int width, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / width;
+  const int c = (int)(idx - t * width);
+  const float gv = to_f32(g[t * ldg + c]);
+  out[t * ldo + c] = from_f32<T>(to_f32(x[t * ldx + c]) / (1.0f + expf(-gv)));
+}
+
+extern "C" int zi_sigmoid_gate(void* out, int ldo, const void* x, int ldx, const void* g, int ldg, int dtype, int T,
+                               int width, cudaStream_t stream) {
+  const size_t total = (size_t)T * width;
+  if (total == 0) return 0;
+  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(sigmoid_gate_kernel<TT>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                                         (TT*)out, ldo, (const TT*)x, ldx, (const TT*)g, ldg, width, total));
+  return zi_check_launch("sigmoid_gate");
+}

@@ -1,0 +1,126 @@
+// Kernels of recurrent mixers: a short causal convolution per channel whose last inputs are carried
+// from step to step, and the real-gated linear recurrence
+//     a_t = exp(-c * r_t * softplus(lam)),  S_t = a_t S_(t-1) + sqrt(1 - a_t^2) * i_t * u_t
+// with its state carried per request.  Everything here is 32-bit arithmetic; only the branch inputs
+// (x and y, the outputs of matrix products) and the result may be bfloat16.
+//
+// The per-request state is one 32-bit array [slots][taps][C]: rows 0 .. taps-2 hold the last taps-1
+// inputs of the convolution (oldest first), row taps-1 holds S.  A request's tokens of this step are
+// rows cu_q[s] .. cu_q[s+1]-1 of the flat batch; they continue the request from the state in slot
+// state_slots[s].  A row is never touched by two blocks, and each channel's tokens are visited in
+// order, so a result does not depend on how the request was cut into steps or on the batch.
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float softplus_f32(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float sigmoid_f32(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// Input of the convolution `back` tokens before token t of request s (back >= 0): from this step's
+// rows if it lies in them, else from the carried rows, else (before the request's start: the carried
+// rows are zero then) zero.
+template <typename T>
+__device__ __forceinline__ float conv_input(const T* __restrict__ x, int ldx, const float* __restrict__ xb,
+                                            const float* __restrict__ st, int C, int taps, int t_local, int tok0,
+                                            int back, int c) {
+  const int src = t_local - back;
+  if (src >= 0) return to_f32(x[(size_t)(tok0 + src) * ldx + c]) + xb[c];
+  const int row = taps - 1 + src;        // src = -1 is the newest carried input: row taps-2
+  return row >= 0 ? st[(size_t)row * C + c] : 0.f;
+}
+
+// u[t, c] = cb[c] + sum_j k[c, j] * input(t - (taps-1-j)), one thread per (token, channel).
+template <typename T>
+__global__ void causal_conv_kernel(float* __restrict__ u, const T* __restrict__ x, int ldx,
+                                   const float* __restrict__ xb, const float* __restrict__ kern,
+                                   const float* __restrict__ cb, const float* __restrict__ state, int C, int taps,
+                                   const int* __restrict__ cu_q, const int* __restrict__ state_slots, int n_seqs) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  int s = 0, hi = n_seqs - 1;          // the request whose rows hold token t: cu_q[s] <= t < cu_q[s+1]
+  while (s < hi) {
+    const int mid = (s + hi + 1) >> 1;
+    if (cu_q[mid] <= t) s = mid; else hi = mid - 1;
+  }
+  const int tok0 = cu_q[s];
+  const float* st = state + (size_t)state_slots[s] * taps * C;
+  float acc = cb[c];
+  for (int j = 0; j < taps; ++j)
+    acc = fmaf(kern[(size_t)c * taps + j], conv_input(x, ldx, xb, st, C, taps, t - tok0, tok0, taps - 1 - j, c), acc);
+  u[(size_t)t * C + c] = acc;
+}
+
+// The recurrence over a request's tokens of this step, one thread per (request, channel).
+// gates [T, blocks, 2, bw] (the products of the block-diagonal gate matrices: recurrence gate, then
+// input gate, per block), rb and ib their biases [C], lam [C], y the gated branch before its bias
+// and gelu.  Writes out[t, c] = S_t * gelu_tanh(y + yb), the new S and the new carried inputs.
+template <typename T>
+__global__ void rglru_scan_kernel(T* __restrict__ out, int ldo, const float* __restrict__ u,
+                                  const float* __restrict__ gates, int bw, const float* __restrict__ rb,
+                                  const float* __restrict__ ib, const float* __restrict__ lam, float decay_scale,
+                                  const T* __restrict__ y, int ldy, const float* __restrict__ yb,
+                                  const T* __restrict__ x, int ldx, const float* __restrict__ xb,
+                                  float* __restrict__ state, int C, int taps, const int* __restrict__ cu_q,
+                                  const int* __restrict__ state_slots) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int s = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int tok0 = cu_q[s], n = cu_q[s + 1] - tok0;
+  if (n <= 0) return;
+  float* st = state + (size_t)state_slots[s] * taps * C;
+  const int b = c / bw, o = c - b * bw;
+  const size_t gcol = (size_t)b * 2 * bw + o;       // recurrence gate; the input gate lies bw further
+  const float rate = -decay_scale * softplus_f32(lam[c]);
+  const float rbias = rb[c], ibias = ib[c], ybias = yb[c];
+  float S = st[(size_t)(taps - 1) * C + c];
+  for (int t = 0; t < n; ++t) {
+    const size_t row = (size_t)(tok0 + t);
+    const float r = sigmoid_f32(gates[row * 2 * C + gcol] + rbias);
+    const float i = sigmoid_f32(gates[row * 2 * C + gcol + bw] + ibias);
+    const float log_a = rate * r;
+    const float a = expf(log_a);
+    const float mult = sqrtf(-expm1f(2.0f * log_a));      // sqrt(1 - a^2) without cancellation near a = 1
+    S = fmaf(a, S, mult * (i * u[row * C + c]));
+    const float yv = gelu_tanh_f32(to_f32(y[row * ldy + c]) + ybias);
+    out[row * ldo + c] = from_f32<T>(S * yv);
+  }
+  st[(size_t)(taps - 1) * C + c] = S;
+  // the last taps-1 inputs of the convolution, oldest first (read before any is overwritten)
+  float keep[8];
+  for (int j = 0; j < taps - 1; ++j) keep[j] = conv_input(x, ldx, xb, st, C, taps, n, tok0, taps - 1 - j, c);
+  for (int j = 0; j < taps - 1; ++j) st[(size_t)j * C + c] = keep[j];
+}
+}  // namespace
+
+extern "C" int zi_causal_conv(float* u, const void* x, int ldx, int dtype, const float* xb, const float* kern,
+                              const float* cb, const float* state, int C, int taps, const int* cu_q,
+                              const int* state_slots, int n_seqs, int T, cudaStream_t stream) {
+  if (T <= 0 || n_seqs <= 0) return 0;
+  if (taps < 1 || taps > 9) return zi_refuse("causal_conv: 1 to 9 taps, got %d", taps);
+  dim3 grid((C + 127) / 128, T);
+  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(causal_conv_kernel<TT>, dim3(grid), dim3(128), 0, stream, u, (const TT*)x, ldx, xb,
+                                         kern, cb, state, C, taps, cu_q, state_slots, n_seqs));
+  return zi_check_launch("causal_conv");
+}
+
+extern "C" int zi_rglru_scan(void* out, int ldo, const float* u, const float* gates, int block_width, const float* rb,
+                             const float* ib, const float* lam, float decay_scale, const void* y, int ldy,
+                             const float* yb, const void* x, int ldx, const float* xb, int dtype, float* state, int C,
+                             int taps, const int* cu_q, const int* state_slots, int n_seqs, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (taps < 1 || taps > 9) return zi_refuse("rglru_scan: 1 to 9 taps, got %d", taps);
+  if (block_width <= 0 || C % block_width) return zi_refuse("rglru_scan: %d channels do not divide into blocks of %d", C, block_width);
+  dim3 grid((C + 127) / 128, n_seqs);
+  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(rglru_scan_kernel<TT>, dim3(grid), dim3(128), 0, stream, (TT*)out, ldo, u, gates,
+                                         block_width, rb, ib, lam, decay_scale, (const TT*)y, ldy, yb, (const TT*)x, ldx,
+                                         xb, state, C, taps, cu_q, state_slots));
+  return zi_check_launch("rglru_scan");
+}
+
+ZI_TRACE_SETTER(recurrent)

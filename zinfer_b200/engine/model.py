@@ -23,13 +23,14 @@ class Run:
     layer: int
     cache: str
     writes: bool
+    pre_add: Optional[tuple[str, int]] = None
 
 
 def _plan_runs(spec: ModelSpec) -> list[Run]:
     runs, seen = [], set()
     for i, e in enumerate(spec.schedule):
         name = e.cache if e.cache is not None else f"run{i}"
-        runs.append(Run(e.layer, name, writes=name not in seen))
+        runs.append(Run(e.layer, name, writes=name not in seen, pre_add=e.pre_add))
         seen.add(name)
     return runs
 
@@ -50,10 +51,12 @@ class DecoderModel:
         self.head = make_part(spec.head, self.ctx)
         self.runs = _plan_runs(spec)
         self._views: list = []
+        self.tables: dict[str, torch.Tensor] = {}
 
     # ----------------------------------------------------------------- weights
     def _final_norm_prefix(self) -> str:
-        return self.spec.final_norm.params.get("name", "norm") + "."
+        params = self.spec.final_norm.params
+        return params["prefix"] if "prefix" in params else params.get("name", "norm") + "."
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         out = dict(self.embedding.tensor_specs())
@@ -61,6 +64,8 @@ class DecoderModel:
             out.update(prefixed(layer.prefix, block.tensor_specs()))
         out.update(prefixed(self._final_norm_prefix(), self.final_norm.tensor_specs()))
         out.update(self.head.tensor_specs())
+        for name, shape in self.spec.tables:
+            out[name] = TensorSpec(tuple(shape))
         return out
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
@@ -71,9 +76,14 @@ class DecoderModel:
         self.head.bind(tensors)
         if getattr(self.head, "tied_to", None) is not None:
             self.head.tie(self.embedding.weight)
+        # vectors added to the 32-bit residual stream are kept in 32-bit
+        self.tables = {name: tensors[name].to(torch.float32).contiguous() for name, _ in self.spec.tables}
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
+        for t in self.tables.values():
+            seen.add(t.data_ptr())
+            total += t.numel() * t.element_size()
         for part in [self.embedding, self.final_norm, self.head, *self.blocks]:
             stack = [part]
             while stack:
@@ -122,7 +132,11 @@ class DecoderModel:
         h = self.embedding.forward(step.token_ids)
         pending = None
         for run, view in zip(self.runs, self._views):
-            pending = self.blocks[run.layer].forward(h, pending, step, view)
+            if run.pre_add is None:
+                pending = self.blocks[run.layer].forward(h, pending, step, view)
+            else:
+                name, row = run.pre_add
+                pending = self.blocks[run.layer].forward(h, pending, step, view, bias=self.tables[name][row])
         if step.logit_rows is None or step.logit_rows.numel() == 0:
             return (None, None) if argmax else None
         x = self.final_norm.forward(h, pending, rows=step.logit_rows)

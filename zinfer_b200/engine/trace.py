@@ -32,6 +32,8 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--max-requests", type=int, default=4,
+                    help="requests that are live at any time: the state slots and block tables the engine holds")
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--poison-freed-pages", action="store_true",
                     help="debugging: overwrite every page with huge values when it is given back")
@@ -46,8 +48,11 @@ def main(argv=None) -> int:
         return 2
     os.makedirs(args.out, exist_ok=True)
     dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[args.dtype]
+    max_tokens = max(args.max_tokens, args.page_size)
+    # no request can grow beyond the pool, so position tables need not reach further either
     runner = ModelRunner.from_model_dir(args.model, dtype=dtype, device=args.device, page_size=args.page_size,
-                                        max_tokens=max(args.max_tokens, args.page_size), max_requests=64,
+                                        max_tokens=max_tokens, max_requests=max(1, args.max_requests),
+                                        max_model_len=-(-max_tokens // args.page_size) * args.page_size,
                                         poison_freed_pages=args.poison_freed_pages)
     for line in sys.stdin:
         line = line.strip()

@@ -147,6 +147,26 @@ class Partials:
         return h if dtype == torch.float32 else h.to(dtype)
 
 
+class Scaled:
+    """An update of the residual stream that is multiplied by ``scale`` as it is added (a model's
+    residual multiplier): ``delta`` is a tensor or :class:`Partials`."""
+
+    def __init__(self, delta, scale: float):
+        self.delta = delta
+        self.scale = float(scale)
+
+    @property
+    def shape(self):
+        return self.delta.shape
+
+
+def _unscaled(delta):
+    """(update, multiplier) of an update given plain or as :class:`Scaled`."""
+    if isinstance(delta, Scaled):
+        return delta.delta, delta.scale
+    return delta, 1.0
+
+
 # ------------------------------------------------------------------ elementwise
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rows ``ids`` of ``table`` [V, H] as the 32-bit residual stream [T, H]."""
@@ -169,14 +189,19 @@ def patch_tokens(ids: torch.Tensor, prev: torch.Tensor, dst: torch.Tensor, src: 
     _check(lib().zi_patch_tokens(_ptr(ids), _ptr(prev), _ptr(dst), _ptr(src), dst.numel(), _stream()), "patch_tokens")
 
 
-def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+def add_rmsnorm(h: torch.Tensor, delta, weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``h += delta`` in place (32-bit), then RMSNorm of every row.
+                out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``h += delta`` in place (32-bit), then RMSNorm of every row.  ``delta`` may be a tensor,
+    :class:`Partials`, or either inside :class:`Scaled` (``h += scale * delta``); ``bias`` (float32 [H])
+    is added to every row as well.
 
     ``rows`` (int32, repeats allowed) picks rows instead: the result has one row per entry,
     the norm of ``h[row] + delta[row]``, and ``h`` is left unchanged."""
     T, H = h.shape
+    delta, dscale = _unscaled(delta)
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == H and bias.is_contiguous(), "the bias is float32 of the row's width")
     _need(h.dtype == torch.float32 and h.is_contiguous(), "the residual stream is contiguous float32")
     _need(weight.dtype == torch.float32 and weight.numel() == H, "norm weight must be float32 of the row's width")
     part, splits, zstride = None, 0, 0
@@ -190,35 +215,63 @@ def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
         out = torch.empty((n, H), dtype=out_dtype, device=h.device)
     with _prof.region("add_rmsnorm", lambda: (2 if rows is None else 1) * n * H * 4 + _nb(out, weight)
                       + (n * H * delta.element_size() if delta is not None else 0) + splits * n * H * 4):
-        _check(lib().zi_add_rmsnorm(_ptr(h), _ptr(delta), _tag(delta) if delta is not None else F32, _ptr(part), splits,
-                                    ctypes.c_longlong(zstride), _ptr(weight), ctypes.c_float(eps), _ptr(out), _tag(out),
-                                    _ptr(rows), n, H, _stream()), "add_rmsnorm")
+        _check(lib().zi_add_rmsnorm_scaled(_ptr(h), _ptr(delta), _tag(delta) if delta is not None else F32, _ptr(part),
+                                           splits, ctypes.c_longlong(zstride), ctypes.c_float(dscale), _ptr(bias),
+                                           _ptr(weight), ctypes.c_float(eps), _ptr(out), _tag(out), _ptr(rows), n, H,
+                                           _stream()), "add_rmsnorm")
     return out
 
 
 def residual_add(h: torch.Tensor, delta) -> None:
+    delta, dscale = _unscaled(delta)
     if isinstance(delta, Partials):
         delta = delta.sum(torch.float32)
     _need(h.dtype == torch.float32 and h.is_contiguous() and delta.is_contiguous() and delta.shape == h.shape,
           "residual_add: shapes must match and be contiguous")
     with _prof.region("residual_add", lambda: 2 * _nb(h) + _nb(delta)):
-        _check(lib().zi_residual_add(_ptr(h), _ptr(delta), _tag(delta), ctypes.c_longlong(h.numel()), _stream()),
-               "residual_add")
+        _check(lib().zi_residual_add_scaled(_ptr(h), _ptr(delta), _tag(delta), ctypes.c_float(dscale),
+                                            ctypes.c_longlong(h.numel()), _stream()), "residual_add")
+
+
+def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """``x *= factor`` in place on a contiguous float32 tensor (a model's multiplier on its logits)."""
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "scale_: a contiguous float32 tensor")
+    with _prof.region("scale", lambda: 2 * _nb(x)):
+        _check(lib().zi_scale_f32(_ptr(x), ctypes.c_longlong(x.numel()), ctypes.c_float(factor), _stream()), "scale")
+    return x
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x * sigmoid(gate)`` for two [T, width] tensors whose rows may be views of wider rows."""
+    T, W = x.shape
+    _need(gate.shape == x.shape and gate.dtype == x.dtype and x.stride(1) == 1 and gate.stride(1) == 1,
+          "sigmoid_gate: two tensors of one shape and type with dense rows")
+    if out is None:
+        out = torch.empty((T, W), dtype=x.dtype, device=x.device)
+    with _prof.region("sigmoid gate", lambda: 3 * T * W * x.element_size()):
+        _check(lib().zi_sigmoid_gate(_ptr(out), out.stride(0), _ptr(x), x.stride(0), _ptr(gate), gate.stride(0), _tag(x),
+                                     T, W, _stream()), "sigmoid_gate")
+    return out
+
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
 
 
 def swiglu(gate_up, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
-           interleave: int = 0) -> torch.Tensor:
-    """``silu(gate) * up`` for ``gate_up`` [T, 2I]: gate then up (``interleave`` 0), or blocks
+           interleave: int = 0, activation: str = "silu") -> torch.Tensor:
+    """``act(gate) * up`` for ``gate_up`` [T, 2I]: gate then up (``interleave`` 0), or blocks
     of 2 * ``interleave`` columns holding ``interleave`` gate values and then the up values of
-    the same features."""
+    the same features.  ``activation``: ``silu`` or ``gelu_tanh`` (the tanh form of gelu)."""
+    _need(activation in ACTIVATIONS, f"unknown activation {activation!r}")
+    act = ACTIVATIONS[activation]
     if isinstance(gate_up, Partials):
         T, two_i = gate_up.shape
         I = two_i // 2
         if I % 4 == 0:
             res = torch.empty((T, I), dtype=out_dtype or torch.bfloat16, device=gate_up.data.device)
             with _prof.region("swiglu (partial sums)", lambda: _nb(res, gate_up.data)):
-                _check(lib().zi_swiglu_partials(_ptr(res), _tag(res), _ptr(gate_up.data), gate_up.splits,
-                                                ctypes.c_longlong(T * two_i), T, I, interleave, _stream()), "swiglu")
+                _check(lib().zi_gated_act_partials(_ptr(res), _tag(res), _ptr(gate_up.data), gate_up.splits,
+                                                   ctypes.c_longlong(T * two_i), T, I, interleave, act, _stream()), "swiglu")
             return res
         gate_up = gate_up.sum(out_dtype or torch.bfloat16)
     T, two_i = gate_up.shape
@@ -227,7 +280,7 @@ def swiglu(gate_up, out: Optional[torch.Tensor] = None, out_dtype: Optional[torc
     if out is None:
         out = torch.empty((T, I), dtype=gate_up.dtype, device=gate_up.device)
     with _prof.region("swiglu", lambda: _nb(out, gate_up)):
-        _check(lib().zi_swiglu(_ptr(out), _ptr(gate_up), _tag(gate_up), T, I, interleave, _stream()), "swiglu")
+        _check(lib().zi_gated_act(_ptr(out), _ptr(gate_up), _tag(gate_up), T, I, interleave, act, _stream()), "swiglu")
     return out
 
 
@@ -366,6 +419,26 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     return out
 
 
+def tensor_core_linear_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether :func:`linear` would run this product on the tcgen05 kernel."""
+    return bool(GEMM_BACKEND != "simt" and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[0] > 0
+                and x.stride(1) == 1 and weight.stride(1) == 1
+                and lib().zi_gemm_tcgen05_supported(_ptr(x), _ptr(weight), x.shape[1], x.stride(0), weight.stride(0)))
+
+
+def linear_cuda_cores(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``x @ weight^T`` with 32-bit multiply-adds on the CUDA cores whatever the operands' types
+    (a router's logits, which are 32-bit also in a bfloat16 run)."""
+    M, K = x.shape
+    N = weight.shape[0]
+    _need(weight.shape[1] == K and x.stride(1) == 1 and weight.is_contiguous(), "linear: operands must be dense along K")
+    out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    with _prof.region(f"linear (CUDA cores) N={N} K={K}", lambda: _nb(weight, out) + M * K * x.element_size(), 2 * M * N * K):
+        _check(lib().zi_gemm_simt(_ptr(out), _tag(out), _ptr(x), _tag(x), _ptr(weight), _tag(weight), M, N, K,
+                                  x.stride(0), weight.stride(0), out.stride(0), _stream()), "linear")
+    return out
+
+
 def linear_argmax(x: torch.Tensor, weight: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """The 32-bit product ``x [M, K] @ weight [N, K]^T`` and each row's argmax (first maximum, NaN
     counted as -inf, as :func:`argmax` has it).  For up to 128 rows on the tensor-core path the
@@ -393,6 +466,190 @@ def linear_argmax(x: torch.Tensor, weight: torch.Tensor) -> tuple[torch.Tensor, 
             return out, ids
     out = linear(x, weight, out_dtype=torch.float32)
     return out, argmax(out)
+
+
+def _ll(v: int):
+    return ctypes.c_longlong(int(v))
+
+
+def linear_batched(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                   relu2: bool = False) -> torch.Tensor:
+    """``batch`` independent products ``out[b] = x[b] @ weight[b]^T`` (+ ``bias[b]``) on the CUDA cores with
+    32-bit multiply-adds: ``x`` [B, M, K], ``weight`` [B, N, K], ``out`` [B, M, N], each possibly a
+    strided view (block-diagonal gate matrices, one projection per head).  Any mix of operand types."""
+    B, M, K = x.shape
+    _need(weight.shape[0] == B and weight.shape[2] == K and out.shape == (B, M, weight.shape[1]), "linear_batched: shapes")
+    N = weight.shape[1]
+    _need(x.stride(2) == 1 and weight.stride(2) == 1 and out.stride(2) == 1, "linear_batched: dense along the last axis")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.shape == (B, N) and bias.is_contiguous(), "linear_batched: bias is float32 [B, N]")
+    with _prof.region(f"linear (CUDA cores, batch of {B}) N={N} K={K}",
+                      lambda: B * (M * K * x.element_size() + N * K * weight.element_size() + M * N * out.element_size()),
+                      2 * B * M * N * K):
+        _check(lib().zi_gemm_simt_general(
+            _ptr(out), _tag(out), _ptr(x), _tag(x), _ptr(weight), _tag(weight), M, N, K, x.stride(1), weight.stride(1),
+            out.stride(1), B, _ll(x.stride(0)), _ll(weight.stride(0)), _ll(out.stride(0)), _ptr(bias), _ll(N), None, None,
+            None, _ll(0), 1 if relu2 else 0, 64 if M > 16 else 16, _stream()), "linear_batched")
+    return out
+
+
+def linear_grouped(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_src: torch.Tensor,
+                   tile_group: torch.Tensor, n_tiles: torch.Tensor, tile_rows: int, relu2: bool = False) -> torch.Tensor:
+    """Products whose sizes only the device knows: output row r is ``x[row_src[r]] @ weight[g]^T`` with g the
+    group (expert) of r's tile of ``tile_rows`` rows (``tile_group``); rows with ``row_src`` -1 and tiles
+    at or beyond ``n_tiles[0]`` are left alone.  ``weight`` [G, N, K]; ``out`` [rows, N]."""
+    G, N, K = weight.shape
+    rows = out.shape[0]
+    _need(x.shape[1] == K and out.shape[1] == N and x.stride(1) == 1 and out.stride(1) == 1 and weight.is_contiguous(),
+          "linear_grouped: shapes")
+    _need(rows % tile_rows == 0 and row_src.numel() >= rows, "linear_grouped: whole tiles of rows")
+    for t, name in ((row_src, "row_src"), (tile_group, "tile_group"), (n_tiles, "n_tiles")):
+        _i32(t, name)
+    with _prof.region(f"linear (CUDA cores, grouped) N={N} K={K}"):
+        _check(lib().zi_gemm_simt_general(
+            _ptr(out), _tag(out), _ptr(x), _tag(x), _ptr(weight), _tag(weight), rows, N, K, x.stride(0), K, out.stride(0),
+            1, _ll(0), _ll(0), _ll(0), None, _ll(0), _ptr(row_src), _ptr(tile_group), _ptr(n_tiles), _ll(N * K),
+            1 if relu2 else 0, tile_rows, _stream()), "linear_grouped")
+    return out
+
+
+# ---------------------------------------------------------------- mixture of experts
+def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int,
+              renormalize: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per token: softmax scores over all router outputs, the ``top`` outputs with the largest score +
+    correction (int32 [T, top]) and their scores without the correction (float32 [T, top]), divided by
+    their sum if ``renormalize``."""
+    T, NR = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "router logits are contiguous float32")
+    if correction is not None:
+        _need(correction.dtype == torch.float32 and correction.numel() == NR, "the correction is float32 [outputs]")
+    chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weight = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    with _prof.region("moe route", lambda: _nb(logits, chosen, weight)):
+        _check(lib().zi_moe_route(_ptr(chosen), _ptr(weight), _ptr(logits), _ptr(correction), T, NR, top,
+                                  1 if renormalize else 0, _stream()), "moe_route")
+    return chosen, weight
+
+
+MOE_TILE_ROWS_SMALL, MOE_TILE_ROWS = 16, 64
+
+
+def moe_align(chosen: torch.Tensor, experts: int, tile_rows: int):
+    """Lays the (token, expert) pairs out by expert in whole tiles of ``tile_rows`` rows.  Returns
+    ``(row_token, row_self, pair_row, tile_expert, n_tiles)``: the token of every row (-1: padding), the
+    row's own index where it is in use, the row of every pair (-1: an identity expert), the expert of
+    every tile and the number of tiles (one int32 on the device)."""
+    T, top = chosen.shape
+    P = T * top
+    cap_tiles = -(-P // tile_rows) + experts
+    dev = chosen.device
+    buf = torch.empty((2 * cap_tiles * tile_rows + P + cap_tiles + 1,), dtype=torch.int32, device=dev)
+    n = cap_tiles * tile_rows
+    row_token, row_self, pair_row = buf[:n], buf[n:2 * n], buf[2 * n:2 * n + P]
+    tile_expert, n_tiles = buf[2 * n + P:2 * n + P + cap_tiles], buf[2 * n + P + cap_tiles:]
+    with _prof.region("moe align", lambda: _nb(chosen) + 3 * P * 4):
+        _check(lib().zi_moe_align(_ptr(_i32(chosen, "chosen")), P, top, experts, tile_rows, _ptr(row_token), _ptr(row_self),
+                                  _ptr(pair_row), _ptr(tile_expert), _ptr(n_tiles), _stream()), "moe_align")
+    return row_token, row_self, pair_row, tile_expert, n_tiles
+
+
+def moe_combine(y: torch.Tensor, x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, pair_row: torch.Tensor,
+                experts: int) -> torch.Tensor:
+    """``out[t] = sum_k weight[t, k] * (y[pair_row[t, k]] if chosen[t, k] < experts else x[t])``, k ascending."""
+    T, H = x.shape
+    top = chosen.shape[1]
+    _need(y.dtype == torch.float32 and y.is_contiguous() and y.shape[1] == H and x.is_contiguous(), "moe_combine: shapes")
+    out = torch.empty((T, H), dtype=x.dtype, device=x.device)
+    with _prof.region("moe combine", lambda: T * top * H * 4 + 2 * _nb(out)):
+        _check(lib().zi_moe_combine(_ptr(out), _ptr(y), _ptr(x), _tag(x), _ptr(chosen), _ptr(weight), _ptr(pair_row), T,
+                                    top, experts, H, _stream()), "moe_combine")
+    return out
+
+
+# ---------------------------------------------------------------- recurrent mixers
+def causal_conv(x: torch.Tensor, x_bias: torch.Tensor, kernel: torch.Tensor, bias: torch.Tensor, state: torch.Tensor,
+                step) -> torch.Tensor:
+    """Per-channel causal convolution of ``x + x_bias`` ([T, C], rows may be views of wider rows) with
+    ``kernel`` [C, taps] (last column: the current token) plus ``bias``; the inputs before a request's
+    first token of this step come from ``state`` [slots, taps, C] (rows 0..taps-2).  Returns float32 [T, C];
+    the state is left as it is (:func:`rglru_scan` carries it on)."""
+    T, C = x.shape
+    taps = kernel.shape[1]
+    _need(x.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
+          and tuple(state.shape[1:]) == (taps, C), "causal_conv: state is float32 [slots, taps, C]")
+    for t in (x_bias, kernel, bias):
+        _need(t.dtype == torch.float32 and t.is_contiguous(), "causal_conv: float32 parameters")
+    u = torch.empty((T, C), dtype=torch.float32, device=x.device)
+    with _prof.region("causal conv", lambda: T * C * (x.element_size() * taps + 4)):
+        _check(lib().zi_causal_conv(_ptr(u), _ptr(x), x.stride(0), _tag(x), _ptr(x_bias), _ptr(kernel), _ptr(bias),
+                                    _ptr(state), C, taps, _ptr(step.cu_q), _ptr(step.state_slots), step.n_seqs, T,
+                                    _stream()), "causal_conv")
+    return u
+
+
+def rglru_scan(u: torch.Tensor, gates: torch.Tensor, block_width: int, r_bias: torch.Tensor, i_bias: torch.Tensor,
+               lam: torch.Tensor, decay_scale: float, y: torch.Tensor, y_bias: torch.Tensor, x: torch.Tensor,
+               x_bias: torch.Tensor, state: torch.Tensor, step) -> torch.Tensor:
+    """The real-gated linear recurrence over each request's tokens of this step, from and to ``state``:
+    ``a = exp(-decay_scale * sigmoid(g_r + r_bias) * softplus(lam))``,
+    ``S = a S + sqrt(1 - a^2) * sigmoid(g_i + i_bias) * u``; returns ``S * gelu_tanh(y + y_bias)`` in ``y``'s
+    type.  ``gates`` float32 [T, blocks, 2, block_width] holds g_r and g_i; ``x`` (the convolution's input
+    before its bias) is read to carry the convolution's last inputs on."""
+    T, C = u.shape
+    taps = state.shape[1]
+    _need(u.dtype == torch.float32 and gates.dtype == torch.float32 and u.is_contiguous() and gates.is_contiguous()
+          and gates.numel() == 2 * T * C, "rglru_scan: u [T, C] and gates [T, 2C] are contiguous float32")
+    _need(y.dtype == x.dtype and y.stride(1) == 1 and x.stride(1) == 1, "rglru_scan: branch rows are dense")
+    out = torch.empty((T, C), dtype=y.dtype, device=y.device)
+    with _prof.region("rglru scan", lambda: T * C * (12 + 3 * y.element_size())):
+        _check(lib().zi_rglru_scan(_ptr(out), out.stride(0), _ptr(u), _ptr(gates), block_width, _ptr(r_bias), _ptr(i_bias),
+                                   _ptr(lam), ctypes.c_float(decay_scale), _ptr(y), y.stride(0), _ptr(y_bias), _ptr(x),
+                                   x.stride(0), _ptr(x_bias), _tag(y), _ptr(state), C, taps, _ptr(step.cu_q),
+                                   _ptr(step.state_slots), step.n_seqs, _stream()), "rglru_scan")
+    return out
+
+
+# ----------------------------------------------------------------- latent attention
+def latent_prepare(proj: torch.Tensor, heads: int, dim: int, rot_dim: int, rank: int, rot_dims: int,
+                   c_weight: torch.Tensor, eps: float, cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor,
+                   q_eff: torch.Tensor, cache: Optional[torch.Tensor], slots: Optional[torch.Tensor]) -> None:
+    """From a token's projections [q heads (dim | rot_dim) | rank | rot_dim | ...]: the rotated query part
+    of every head goes to ``q_eff[t, h, rank:]``; the RMS-normed latent and the rotated key part go into
+    the token's cache row (``cache`` [pages, 1, page_size, rank + rot_dim], row ``slots[t]``)."""
+    T = proj.shape[0]
+    D = rank + rot_dim
+    _need(proj.stride(1) == 1 and proj.shape[1] >= heads * (dim + rot_dim) + D, "latent_prepare: projection rows")
+    _need(q_eff.is_contiguous() and q_eff.dtype == proj.dtype and q_eff.numel() == T * heads * D, "latent_prepare: q_eff")
+    _need(c_weight.dtype == torch.float32 and c_weight.numel() == rank, "latent_prepare: the latent's norm weight")
+    _need(cos.dtype == torch.float32 and cos.shape == sin.shape and cos.shape[1] == rot_dims // 2, "latent_prepare: tables")
+    if cache is not None:
+        _need(cache.is_contiguous() and cache.dtype == proj.dtype and cache.shape[-1] == D and cache.shape[1] == 1,
+              "latent_prepare: cache rows")
+        _i32(slots, "slots")
+    with _prof.region("latent prepare", lambda: 2 * T * (heads * rot_dim + D) * proj.element_size()):
+        _check(lib().zi_latent_prepare(_ptr(proj), proj.stride(0), _tag(proj), T, heads, dim, rot_dim, rank, rot_dims,
+                                       _ptr(c_weight), ctypes.c_float(eps), _ptr(cos), _ptr(sin), cos.shape[0],
+                                       _ptr(_i32(positions, "positions")), _ptr(q_eff), _ptr(cache), _ptr(slots),
+                                       1 if cache is not None else 0, _stream()), "latent_prepare")
+
+
+def latent_attention(q_eff: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, step, heads: int, rank: int,
+                     page_size: int, window: Optional[int], scale: float) -> torch.Tensor:
+    """Causal softmax attention of ``q_eff`` [T, heads * D] over the latent rows of each request's pages
+    (``cache`` [pages, 1, page_size, D]): scores over all D columns, values the first ``rank`` columns.
+    Returns [T, heads * rank].  32-bit arithmetic on the CUDA cores."""
+    T = q_eff.shape[0]
+    D = cache.shape[-1]
+    _need(q_eff.shape[1] == heads * D and q_eff.is_contiguous() and cache.is_contiguous() and cache.dtype == q_eff.dtype,
+          "latent_attention: shapes")
+    out = torch.empty((T, heads * rank), dtype=q_eff.dtype, device=q_eff.device)
+    with _prof.region("latent attention (exact, CUDA cores)"):
+        _check(lib().zi_paged_attention_v(
+            _ptr(out), out.stride(0), _ptr(q_eff), q_eff.stride(0), _tag(q_eff), _ptr(cache), _ptr(cache),
+            _ptr(_i32(block_tables, "block_tables")), block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens),
+            _ptr(step.tile_seq), _ptr(step.tile_q0), step.tile_seq.shape[0], heads, 1, D, rank, D, page_size,
+            int(window or 0), ctypes.c_float(scale), _stream()), "latent_attention")
+    return out
 
 
 # ----------------------------------------------------------------------- attention

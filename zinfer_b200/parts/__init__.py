@@ -3,17 +3,22 @@ from .base import (Block, BuildContext, FeedForward, KVCacheNeed, Mixer, Norm, P
 from .attention import GQAttention
 from .block import PreNormBlock
 from .embedding import LMHead, TokenEmbedding
+from .latent_attention import LatentAttention
 from .mlp import SwiGLUMLP
+from .moe import RoutedExperts
 from .norm import RMSNorm
+from .rglru import RGLRUMixer
 from .rope import NoPosition, RotaryPosition
 
 for _kind, _cls in (("rmsnorm", RMSNorm), ("rope", RotaryPosition), ("no_position", NoPosition),
                     ("gqa_attention", GQAttention), ("swiglu_mlp", SwiGLUMLP), ("prenorm_block", PreNormBlock),
-                    ("token_embedding", TokenEmbedding), ("lm_head", LMHead)):
+                    ("token_embedding", TokenEmbedding), ("lm_head", LMHead), ("latent_attention", LatentAttention),
+                    ("rglru", RGLRUMixer), ("routed_experts", RoutedExperts)):
     register_part(_kind, _cls, replace=True)
 
 __all__ = [
-    "Block", "BuildContext", "FeedForward", "GQAttention", "KVCacheNeed", "LMHead", "Mixer", "NoPosition", "Norm",
-    "Part", "PositionEncoding", "PreNormBlock", "RMSNorm", "RotaryPosition", "StateNeed", "SwiGLUMLP", "TensorSpec",
+    "Block", "BuildContext", "FeedForward", "GQAttention", "KVCacheNeed", "LMHead", "LatentAttention", "Mixer",
+    "NoPosition", "Norm", "Part", "PositionEncoding", "PreNormBlock", "RGLRUMixer", "RMSNorm", "RotaryPosition",
+    "RoutedExperts", "StateNeed", "SwiGLUMLP", "TensorSpec",
     "TokenEmbedding", "make_part", "prefixed", "register_part", "take", "unregister_part",
 ]

@@ -7,18 +7,21 @@ them by name.
 
 Kinds of part and what each must provide:
 
-``Norm``            ``forward(h, delta, rows=None)``: adds ``delta`` (may be None) into
-                    the 32-bit residual ``h`` in place and returns the normed rows in
-                    the activation dtype; with ``rows`` it returns the norm of the
-                    picked rows of ``h + delta`` and leaves ``h`` alone.
+``Norm``            ``forward(h, delta, rows=None, bias=None)``: adds ``delta`` (may be None;
+                    a tensor, split-K partial sums, or either with a multiplier as
+                    ``ops.Scaled``) and the vector ``bias`` into the 32-bit residual ``h``
+                    in place and returns the normed rows in the activation dtype; with
+                    ``rows`` it returns the norm of the picked rows of ``h + delta`` and
+                    leaves ``h`` alone.
 ``PositionEncoding````tables()``: what the mixer's kernels need to place a token.
 ``Mixer``           ``cache_need()``: a :class:`KVCacheNeed`, a :class:`StateNeed`
                     or None; ``forward(x, step, cache)`` mixes tokens of the same
                     request, reading and writing only its own cache.
 ``FeedForward``     ``forward(x)``: works on each token alone.
-``Block``           ``mixer`` attribute and ``forward(h, pending, step, cache)``:
+``Block``           ``mixer`` attribute and ``forward(h, pending, step, cache, bias=None)``:
                     arranges norms, mixer, feed-forward and residual sums; returns
-                    the update not yet added into ``h``.
+                    the update not yet added into ``h``.  ``bias`` is a vector the model
+                    adds to the residual stream right before this run of the layer.
 """
 from __future__ import annotations
 
@@ -48,11 +51,13 @@ class TensorSpec:
 class KVCacheNeed:
     """Keys and values per token in pages.  ``window`` None: every earlier key stays
     visible; an integer w: a query at position i reads keys i-w+1 .. i, and pages
-    wholly behind that may be given back."""
+    wholly behind that may be given back.  ``values`` False: the pages hold keys only (a mixer
+    whose values are part of its key rows, such as a latent shared by keys and values)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    values: bool = True
 
 
 @dataclass(frozen=True)
@@ -86,7 +91,8 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, delta, rows: Optional[torch.Tensor] = None,
+                bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -115,7 +121,7 @@ class FeedForward(Part):
 class Block(Part):
     mixer: Mixer
 
-    def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], step, cache) -> Optional[torch.Tensor]:
+    def forward(self, h: torch.Tensor, pending, step, cache, bias: Optional[torch.Tensor] = None):
         raise NotImplementedError
 
 

@@ -15,45 +15,50 @@ class TokenEmbedding(Part):
         super().__init__(params, ctx)
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
-        self.name = params.get("name", "embed_tokens")
+        self.name = params.get("name", "embed_tokens") + params.get("suffix", ".weight")
         self.weight = None
 
     def tensor_specs(self):
-        return {self.name + ".weight": TensorSpec((self.vocab, self.hidden))}
+        return {self.name: TensorSpec((self.vocab, self.hidden))}
 
     def bind(self, tensors):
-        self.weight = tensors[self.name + ".weight"].contiguous()
+        self.weight = tensors[self.name].contiguous()
 
     def forward(self, token_ids):
         return ops.embed_gather(self.weight, token_ids)
 
 
 class LMHead(Part):
-    """logits = W x in 32-bit.  ``tied_to`` names the embedding whose table stands
-    for W; a separate ``<name>.weight`` in the file is then optional and unused."""
+    """logits = scale * W x in 32-bit (``scale`` 1 unless the model gives one).  ``tied_to`` names the
+    embedding whose table stands for W; a separate ``<name>.weight`` in the file is then optional and unused."""
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
-        self.name = params.get("name", "lm_head")
+        self.name = params.get("name", "lm_head") + params.get("suffix", ".weight")
         self.tied_to = params.get("tied_to")
+        self.scale = float(params.get("scale", 1.0))
         self.weight = None
 
     def tensor_specs(self):
-        return {self.name + ".weight": TensorSpec((self.vocab, self.hidden), optional=self.tied_to is not None)}
+        return {self.name: TensorSpec((self.vocab, self.hidden), optional=self.tied_to is not None)}
 
     def bind(self, tensors):
         if self.tied_to is None:
-            self.weight = tensors[self.name + ".weight"].contiguous()
+            self.weight = tensors[self.name].contiguous()
 
     def tie(self, table: torch.Tensor):
         self.weight = table
 
     def forward(self, x):
-        return ops.linear(x, self.weight, out_dtype=torch.float32)
+        logits = ops.linear(x, self.weight, out_dtype=torch.float32)
+        return logits if self.scale == 1.0 else ops.scale_(logits, self.scale)
 
     def forward_argmax(self, x):
         """The logits and each row's first maximum, found in the product's own epilogue where the
         tensor-core kernel takes the shape."""
-        return ops.linear_argmax(x, self.weight)
+        if self.scale == 1.0:
+            return ops.linear_argmax(x, self.weight)
+        logits = self.forward(x)
+        return logits, ops.argmax(logits)

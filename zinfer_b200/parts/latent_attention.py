@@ -1,0 +1,111 @@
+"""Latent attention: keys and values of all heads are linear maps of one small latent per token
+(the multi-head latent attention of "DeepSeek-V2: A Strong, Economical, and Efficient
+Mixture-of-Experts Language Model", DeepSeek-AI, 2024).
+
+From the input h:  q = W_q h, per head [``dim`` plain | ``rot_dim`` rotated];  W_dkv h gives
+``kv_rank`` values, RMS-normed into the latent c, and ``rot_dim`` values that are rotated and
+serve every head as the rotated key part.  Head n has the key [W_uk,n c | rotated part] and the
+value W_uv,n c; its score is (q_plain . k_plain + q_rot . k_rot) * scale, causal, plain softmax.
+The concatenated heads may be gated by sigmoid(W_g h); W_o follows.
+
+Only [c | rotated key part] is cached: one row of kv_rank + rot_dim values per token, in pages of
+keys only.  The attention runs in the folded form: q_lat,n = W_uk,n^T q_plain,n, so that the score
+is [q_lat,n | q_rot,n] . row, the weighted sum runs over the rows' c parts, and W_uv,n is applied
+to that sum: every cached row is read once for all heads, as key and as value.
+
+Rotary positions turn the first ``rot_dims`` of the rot_dim values (pairs (i, i + rot_dims/2)).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import KVCacheNeed, Mixer, TensorSpec, make_part
+
+
+class LatentAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden = int(params["hidden_size"])
+        self.heads = int(params["num_heads"])
+        self.dim = int(params["dim"])
+        self.rot_dim = int(params["rot_dim"])
+        self.vdim = int(params["vdim"])
+        self.rank = int(params["kv_rank"])
+        self.scale = float(params["scale"])
+        self.eps = float(params["norm_eps"])
+        self.gated = bool(params.get("output_gate", False))
+        self.window = params.get("window")
+        self.position = make_part(params["position"], ctx)
+        self.rot_dims = int(getattr(self.position, "head_dim", self.rot_dim))
+        if self.rot_dims > self.rot_dim or self.rot_dims % 2:
+            raise ValueError(f"{self.rot_dims} rotated dimensions do not fit the rotated part of {self.rot_dim}")
+        self.row = self.rank + self.rot_dim          # a cached row
+        if self.row > 640:
+            raise ValueError(f"cached rows of {self.row} values are wider than the attention kernel takes (640)")
+
+    # ------------------------------------------------------------------ weights
+    def tensor_specs(self):
+        H, hid = self.heads, self.hidden
+        specs = {
+            "q": TensorSpec((H * (self.dim + self.rot_dim), hid)),
+            "dkv": TensorSpec((self.row, hid)),
+            "dkv.norm": TensorSpec((self.rank,), init="norm"),
+            "uk": TensorSpec((H * self.dim, self.rank)),
+            "uv": TensorSpec((H * self.vdim, self.rank)),
+            "o": TensorSpec((hid, H * self.vdim)),
+        }
+        if self.gated:
+            specs["g"] = TensorSpec((H * self.vdim, hid))
+        return specs
+
+    def bind(self, tensors):
+        parts = [tensors["q"], tensors["dkv"]] + ([tensors["g"]] if self.gated else [])
+        if len({p.dtype for p in parts}) > 1:
+            parts = [p.to(torch.float32) for p in parts]
+        self.w_in = torch.cat(parts, dim=0).contiguous()      # one product: queries, latent, gate
+        self.c_norm = tensors["dkv.norm"].to(torch.float32).contiguous()
+        H = self.heads
+        # per head the key map transposed, [rank, dim]: q_lat = q_plain @ W_uk,n
+        self.w_uk_t = tensors["uk"].view(H, self.dim, self.rank).transpose(1, 2).contiguous()
+        self.w_uv = tensors["uv"].view(H, self.vdim, self.rank).contiguous()
+        self.w_o = tensors["o"].contiguous()
+
+    # -------------------------------------------------------------------- cache
+    def cache_need(self):
+        return KVCacheNeed(num_kv_heads=1, head_dim=self.row, window=self.window, values=False)
+
+    def max_positions(self):
+        return getattr(self.position, "n_positions", None)
+
+    # ------------------------------------------------------------------ forward
+    def _per_head(self, x, weight, out):
+        """out[:, n] = x[:, n] @ weight[n]^T for every head n (views [T, heads, *])."""
+        if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and ops.tensor_core_linear_ok(x[:, 0], weight[0]):
+            for n in range(self.heads):
+                ops.linear(x[:, n], weight[n], out=out[:, n])
+        else:
+            ops.linear_batched(x.transpose(0, 1), weight, out.transpose(0, 1))
+        return out
+
+    def forward(self, x, step, cache):
+        T, H, D = x.shape[0], self.heads, self.row
+        qw = H * (self.dim + self.rot_dim)
+        proj = ops.linear(x, self.w_in, out_dtype=self.ctx.dtype)
+        group = step.kv_groups[cache.group]
+        cos, sin = self.position.tables()
+        q_eff = torch.empty((T, H, D), dtype=self.ctx.dtype, device=x.device)
+        ops.latent_prepare(proj, H, self.dim, self.rot_dim, self.rank, self.rot_dims, self.c_norm, self.eps, cos, sin,
+                           step.positions, q_eff, cache.k if cache.writes else None, group.slot_mapping)
+        q_plain = proj[:, :qw].view(T, H, self.dim + self.rot_dim)[:, :, :self.dim]
+        self._per_head(q_plain, self.w_uk_t, q_eff[:, :, :self.rank])
+        lat = ops.latent_attention(q_eff.view(T, H * D), cache.k, group.block_tables, step, H, self.rank,
+                                   cache.page_size, self.window, self.scale)
+        heads = torch.empty((T, H, self.vdim), dtype=self.ctx.dtype, device=x.device)
+        self._per_head(lat.view(T, H, self.rank), self.w_uv, heads)
+        heads = heads.view(T, H * self.vdim)
+        if self.gated:
+            heads = ops.sigmoid_gate(heads, proj[:, qw + D:qw + D + H * self.vdim], out=heads)
+        return ops.linear(heads, self.w_o, out_dtype=self.ctx.dtype, allow_partials=True)

@@ -1,6 +1,8 @@
-"""Dense SwiGLU feed-forward: down(silu(gate(x)) * up(x))
-(src/model/runtime/optimized_decoder/layer.zig:193-197, src/kernel/core/cpu.zig:130-147).
-gate and up are stored as one matrix [2I, H] so one product feeds both."""
+"""Dense gated feed-forward: down(act(gate(x)) * up(x)), act = silu (SwiGLU:
+src/model/runtime/optimized_decoder/layer.zig:193-197, src/kernel/core/cpu.zig:130-147) or,
+with ``activation: gelu_tanh``, the tanh form of gelu.  gate and up are stored as one matrix
+[2I, H] so one product feeds both.  ``names`` gives the three tensors' names (gate, up, down)
+where a model calls them otherwise."""
 from __future__ import annotations
 
 import torch
@@ -14,31 +16,37 @@ class SwiGLUMLP(FeedForward):
         super().__init__(params, ctx)
         self.hidden = int(params["hidden_size"])
         self.inter = int(params["intermediate_size"])
+        self.activation = str(params.get("activation", "silu"))
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation {self.activation!r}")
+        self.names = tuple(params.get("names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
         self.w_gate_up = None
         self.w_down = None
 
     def tensor_specs(self):
+        gate, up, down = self.names
         return {
-            "gate_proj.weight": TensorSpec((self.inter, self.hidden)),
-            "up_proj.weight": TensorSpec((self.inter, self.hidden)),
-            "down_proj.weight": TensorSpec((self.hidden, self.inter)),
+            gate: TensorSpec((self.inter, self.hidden)),
+            up: TensorSpec((self.inter, self.hidden)),
+            down: TensorSpec((self.hidden, self.inter)),
         }
 
     def bind(self, tensors):
-        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        g, u = tensors[self.names[0]], tensors[self.names[1]]
         if g.dtype != u.dtype:
             g, u = g.to(torch.float32), u.to(torch.float32)
         # rows interleaved in blocks of 64 (gate block, up block) when the width allows it: the
         # tensor-core product can then apply the SwiGLU in its epilogue
         self.interleaved = self.inter % ops.SWIGLU_INTERLEAVE == 0
         self.w_gate_up = ops.interleave_gate_up(g, u) if self.interleaved else torch.cat([g, u], dim=0).contiguous()
-        self.w_down = tensors["down_proj.weight"].contiguous()
+        self.w_down = tensors[self.names[2]].contiguous()
 
     def forward(self, x):
-        if self.interleaved:
+        if self.interleaved and self.activation == "silu":
             act = ops.linear_swiglu(x, self.w_gate_up, out_dtype=self.ctx.dtype)
-        else:
+        else:    # the product's fused epilogue knows silu only
             gu = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype, allow_partials=True)
-            act = ops.swiglu(gu, out_dtype=self.ctx.dtype)
+            act = ops.swiglu(gu, out_dtype=self.ctx.dtype, activation=self.activation,
+                             interleave=ops.SWIGLU_INTERLEAVE if self.interleaved else 0)
         # the product may come back as split-K partial sums; the next norm adds them with the residual
         return ops.linear(act, self.w_down, out_dtype=self.ctx.dtype, allow_partials=True)

@@ -1,0 +1,74 @@
+"""Mixture of experts: every token runs ``top`` of ``experts`` small feed-forwards and takes the
+weighted sum of their outputs.
+
+Router: logits z = W_r h over ``experts + identity`` outputs in 32-bit, scores s = softmax(z)
+(``sigmoid`` is not built).  A token chooses the ``top`` outputs with the largest s + correction
+(a per-output vector; the selection bias of auxiliary-loss-free balancing) and weights them by
+s without the correction, divided by their sum only if ``renormalize``.  The last ``identity``
+outputs stand for experts without weights whose output is their input.  An expert is
+W_down act(W_up h) with act the square of relu (``relu2``).
+
+The chosen (token, expert) pairs are laid out by expert on the device, in whole tiles, and two
+grouped products run over them; nothing is read back, so a decode step can be captured.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import FeedForward, TensorSpec
+
+
+class RoutedExperts(FeedForward):
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.experts = int(params["experts"])
+        self.identity = int(params.get("identity_experts", 0))
+        self.top = int(params["top"])
+        self.renormalize = bool(params.get("renormalize", False))
+        self.has_correction = bool(params.get("correction", False))
+        act = params.get("activation", "relu2")
+        if act != "relu2":
+            raise ValueError(f"experts with activation {act!r} are not built (relu2 is)")
+        if params.get("score", "softmax") != "softmax":
+            raise ValueError("router scores other than softmax are not built")
+        self.outputs = self.experts + self.identity
+        if not 1 <= self.top <= self.outputs:
+            raise ValueError(f"{self.top} of {self.outputs} router outputs cannot be chosen")
+        self.expert_names = params.get("expert_names", "e{}.")     # prefix of expert i's tensors
+
+    def tensor_specs(self):
+        specs = {"router": TensorSpec((self.outputs, self.hidden))}
+        if self.has_correction:
+            specs["correction"] = TensorSpec((self.outputs,), init="zeros")
+        for e in range(self.experts):
+            p = self.expert_names.format(e)
+            specs[p + "up"] = TensorSpec((self.inter, self.hidden))
+            specs[p + "down"] = TensorSpec((self.hidden, self.inter))
+        return specs
+
+    def bind(self, tensors):
+        self.w_router = tensors["router"].contiguous()
+        self.correction = tensors["correction"].to(torch.float32).contiguous() if self.has_correction else None
+        ups = [tensors[self.expert_names.format(e) + "up"] for e in range(self.experts)]
+        downs = [tensors[self.expert_names.format(e) + "down"] for e in range(self.experts)]
+        if len({t.dtype for t in ups + downs}) > 1:
+            ups, downs = [t.to(torch.float32) for t in ups], [t.to(torch.float32) for t in downs]
+        dev = self.w_router.device
+        self.w_up = torch.stack(ups).contiguous() if ups else torch.empty((0, self.inter, self.hidden), device=dev)
+        self.w_down = torch.stack(downs).contiguous() if downs else torch.empty((0, self.hidden, self.inter), device=dev)
+
+    def forward(self, x):
+        T = x.shape[0]
+        logits = ops.linear_cuda_cores(x, self.w_router, out_dtype=torch.float32)     # 32-bit multiply-adds
+        chosen, weight = ops.moe_route(logits, self.correction, self.top, self.renormalize)
+        tile = ops.MOE_TILE_ROWS if T * self.top > 16 * max(self.experts, 1) else ops.MOE_TILE_ROWS_SMALL
+        row_token, row_self, pair_row, tile_expert, n_tiles = ops.moe_align(chosen, self.experts, tile)
+        rows = row_token.numel()
+        mid = torch.empty((rows, self.inter), dtype=self.ctx.dtype, device=x.device)
+        ops.linear_grouped(x, self.w_up, mid, row_token, tile_expert, n_tiles, tile, relu2=True)
+        y = torch.empty((rows, self.hidden), dtype=torch.float32, device=x.device)
+        ops.linear_grouped(mid, self.w_down, y, row_self, tile_expert, n_tiles, tile)
+        return ops.moe_combine(y, x, chosen, weight, pair_row, self.experts)

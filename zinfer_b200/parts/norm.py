@@ -16,16 +16,17 @@ class RMSNorm(Norm):
         super().__init__(params, ctx)
         self.size = int(params["size"])
         self.eps = float(params["eps"])
+        self.tensor = str(params.get("tensor", "weight"))   # the weight's name relative to the part
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self):
-        return {"weight": TensorSpec((self.size,), init="norm")}
+        return {self.tensor: TensorSpec((self.size,), init="norm")}
 
     def bind(self, tensors):
         # norm vectors are widened to 32-bit once, as the reference does
         # (src/model/runtime/optimized_decoder/support.zig:6-19)
-        self.weight = tensors["weight"].to(torch.float32).contiguous()
+        self.weight = tensors[self.tensor].to(torch.float32).contiguous()
 
-    def forward(self, h, delta, rows=None):
-        """Adds ``delta`` into the residual ``h`` in place, then norms (the picked rows)."""
-        return ops.add_rmsnorm(h, delta, self.weight, self.eps, self.ctx.dtype, rows=rows)
+    def forward(self, h, delta, rows=None, bias=None):
+        """Adds ``delta`` (and ``bias``) into the residual ``h`` in place, then norms (the picked rows)."""
+        return ops.add_rmsnorm(h, delta, self.weight, self.eps, self.ctx.dtype, rows=rows, bias=bias)
