@@ -120,7 +120,7 @@ def route(h, w, p, router):
     return chosen, torch.gather(s, 1, chosen)
 
 
-def moe_ff(h, w, p, mlp, margins=None):
+def moe_ff(h, w, p, mlp, margins=None, last_only=False):
     """Mixture of experts: expert e is W_down relu(W_up h)^2; the last ``identity`` router
     outputs stand for experts that return h itself."""
     router = mlp["router"]
@@ -128,8 +128,10 @@ def moe_ff(h, w, p, mlp, margins=None):
     chosen, weight = route(h, w, p, router)
     if margins is not None:   # how clearly the chosen set beat the best expert left out
         s = torch.softmax(h @ w[p + "router"].T, dim=-1) + w[p + "correction"]
-        top = torch.topk(s, router["top"] + 1, dim=-1).values
-        margins.append((top[:, -2] - top[:, -1]).min().item())
+        if router["top"] < s.shape[-1]:
+            top = torch.topk(s, router["top"] + 1, dim=-1).values
+            gap = top[:, -2] - top[:, -1]
+            margins.append((gap[-1] if last_only else gap.min()).item())
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, g in zip(chosen[t].tolist(), weight[t]):
@@ -157,9 +159,10 @@ def layer_runs(cfg):
     return runs
 
 
-def forward(cfg, w, tokens, residuals=None, margins=None):
+def forward(cfg, w, tokens, residuals=None, margins=None, last_only_margins=False):
     """Logits [S, vocab] of a whole sequence.  ``residuals`` (a list) receives the residual
-    stream after every layer run."""
+    stream after every layer run; ``margins`` (a list) how clearly each routed layer run chose
+    (over all positions, or the last one only)."""
     eps, m = cfg["norm"]["eps"], cfg["residual_mult"]
     x = w["embed"][torch.as_tensor(tokens)]
     for i, t, first in layer_runs(cfg):
@@ -177,7 +180,8 @@ def forward(cfg, w, tokens, residuals=None, margins=None):
         mlp = layer.get("mlp")
         if mlp is not None:
             hin = rmsnorm(x, w[p + "norm2"], eps)
-            ff = dense_ff(hin, w, p + "mlp.") if mlp["kind"] == "dense" else moe_ff(hin, w, p + "mlp.", mlp, margins)
+            ff = dense_ff(hin, w, p + "mlp.") if mlp["kind"] == "dense" else \
+                moe_ff(hin, w, p + "mlp.", mlp, margins, last_only_margins)
             x = x + m * ff
         if residuals is not None:
             residuals.append(x.clone())

@@ -503,9 +503,18 @@ def test_tensor_core_attention_finds_one_far_key_and_ignores_stale_pages():
 
 def test_attention_refuses_what_it_cannot_do():
     o = ops()
-    args = _paged_case(torch.float32, 2, 1, 272, 16, [1], [3])
+    args = _paged_case(torch.float32, 2, 1, 642, 16, [1], [3])      # rows of up to 640 values are taken
     with pytest.raises(o.KernelError, match="head_dim"):
         o.paged_attention(window=None, scale=1.0, **args)
+
+
+def test_exact_attention_takes_wide_heads():
+    """Heads wider than 256 (the rows of a latent cache) go through the exact kernel's wide form."""
+    o = ops()
+    args = _paged_case(torch.float32, 2, 1, 272, 16, [1, 5], [3, 40])
+    got = o.paged_attention(window=None, scale=0.06, **args)
+    want = ref.paged_attention(window=None, scale=0.06, **args)
+    torch.testing.assert_close(got, want, rtol=2e-5, atol=2e-6)
 
 
 @pytest.mark.parametrize("R,V", [(1, 301), (5, 151936), (64, 1000)])
