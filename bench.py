@@ -116,6 +116,119 @@ def matmul_params(cfg, n_layers: int) -> int:
     return n_layers * per_layer
 
 
+# ------------------------------------------------------------ another design beside Qwen3
+def luvavik_shape(width: int, heads: int, experts: int, top: int, expert_ff: int, dense_ff: int) -> dict:
+    """A Luvavik configuration with layers the size of a real model's: latent attention with heads of
+    128 + 64 rotated dimensions over a latent of 512, recurrent blocks as wide as the model in blocks of
+    128 channels with four taps, a dense feed-forward in the first layer and experts elsewhere; layers
+    1..2 run twice.  Seven layer runs in all."""
+    attn = {"type": "latent_attention",
+            "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+                      "rot": {"base": 10000.0, "dims": 64}}}
+    rec = {"type": "rglru", "mixer": {"width": width, "blocks": width // 128, "conv": 4}}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top, "identity": 2}}
+    dense = {"kind": "dense", "ff": dense_ff}
+    layers = [dict(attn, mlp=dense), dict(rec, mlp=moe), dict(attn, mlp=moe), dict(attn, mlp=moe), dict(rec, mlp=moe)]
+    return {"architecture": "Luvavik", "vocab": 32768, "width": width, "layers": layers, "norm": {"eps": 1e-6},
+            "residual_mult": 0.5, "logit_scale": 1.0, "loop": {"start": 1, "stop": 3, "times": 2},
+            "max_position_embeddings": 8192}
+
+
+DESIGN_SIZES = {
+    # name: (width, heads, experts, chosen, expert ff, dense ff); Qwen3 beside it: the same width, layer runs and
+    # heads of 128, a feed-forward as wide as the chosen experts together (equal products per token)
+    "2048": (2048, 16, 16, 4, 1024, 5632),
+    "4096": (4096, 32, 32, 4, 2048, 11264),
+}
+
+
+def compare_designs(args) -> int:
+    """Prefill and decode throughput of the Luvavik design at layer sizes of real models, beside Qwen3
+    dense at equal width, layer count and products per token; with --profile the per-kernel-class times
+    and roofline fractions of both.  Prints one JSON line of its own (the default benchmark is untouched)."""
+    import torch
+    from zinfer_b200 import ops
+    from zinfer_b200.config import LuvavikConfig, Qwen3Config
+    from zinfer_b200.engine import StepEntry
+    from zinfer_b200.engine.api import Engine
+
+    hbm_gbs, bf16_tflops, peak_src = peaks()
+    gen = torch.Generator().manual_seed(99)
+    steps, warmup, batch = args.steps, max(3, args.warmup), args.batch
+    tokens, context = 2048, 2048
+    results, profiles = {}, {}
+
+    def event_ms(fn, n):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(n):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / n
+
+    def measure(name, cfg, vocab):
+        engine = Engine(config=cfg, random_weights_seed=7, dtype="bfloat16", device="cuda:0", page_size=16,
+                        kv_cache_tokens=batch * (context + steps + warmup + 64) + tokens + 64,
+                        max_batched_tokens=tokens, max_requests=batch, max_model_len=8192)
+        runner = engine.runner
+        rand = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+        prompt = rand(tokens)
+
+        def prefill_once():
+            runner.step([StepEntry("prefill", prompt, [tokens - 1])])
+            runner.end_request("prefill")
+
+        for _ in range(2):
+            prefill_once()
+        pf_ms = event_ms(prefill_once, 3)
+        ids = [f"d{i}" for i in range(batch)]
+        for rid in ids:
+            runner.step([StepEntry(rid, rand(context), [])])
+        cur = rand(batch)
+        one = lambda: runner.step_argmax([StepEntry(rid, [t], [0]) for rid, t in zip(ids, cur)])
+        for _ in range(warmup):
+            one()
+        dec_ms = event_ms(one, steps)
+        out = {"prefill_tokens_per_s": round(tokens / (pf_ms * 1e-3), 1), "prefill_ms": round(pf_ms, 3),
+               "decode_tokens_per_s": round(batch / (dec_ms * 1e-3), 1), "decode_ms_per_step": round(dec_ms, 4),
+               "weight_gb": round(runner.model.weight_bytes() / 1e9, 3)}
+        if args.profile:
+            with engine.profile(hbm_gbs, bf16_tflops) as prof:
+                for _ in range(3):
+                    one()
+                dec = prof.summary()
+            with engine.profile(hbm_gbs, bf16_tflops) as prof:
+                prefill_once()
+                pf = prof.summary()
+            profiles[name] = {"decode": dec, "prefill": pf}
+        for rid in ids:
+            runner.end_request(rid)
+        ops.require_kernel_status_ok(name)
+        del engine, runner
+        torch.cuda.empty_cache()
+        return out
+
+    for size in (args.design_sizes.split(",") if args.design_sizes else DESIGN_SIZES):
+        width, heads, experts, top, eff, dff = DESIGN_SIZES[size]
+        raw = luvavik_shape(width, heads, experts, top, eff, dff)
+        results[f"luvavik_{size}"] = measure(f"luvavik_{size}", LuvavikConfig.from_dict(raw), raw["vocab"])
+        # two products of an expert against three of the gated feed-forward: equal multiply-adds per token
+        qwen = dict(QWEN3_8B, vocab_size=raw["vocab"], hidden_size=width, intermediate_size=(2 * top * eff) // 3 // 64 * 64,
+                    num_hidden_layers=7, num_attention_heads=heads, num_key_value_heads=max(1, heads // 4), head_dim=128,
+                    max_position_embeddings=8192)
+        results[f"qwen3_{size}"] = measure(f"qwen3_{size}", Qwen3Config.from_dict(qwen), raw["vocab"])
+    if args.profile:
+        with open(args.profile, "w") as f:
+            json.dump(profiles, f, indent=1)
+    print(json.dumps({"metric": "prefill and decode tokens/s, Luvavik beside Qwen3 dense at equal width and layer runs",
+                      "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16",
+                      "data": "synthetic", "config": {"prefill_tokens": tokens, "decode_batch": batch, "context": context,
+                                                      "layer_runs": 7, "peaks": peak_src}, "results": results}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -132,8 +245,14 @@ def main() -> int:
                     help="with ZINFER_B200_TRACE=1 in the environment: write the timeline of one decode step at the "
                          "headline batch (every kernel's start, the completion of what it depends on, and what it adds "
                          "to the chain) there as JSON, and do nothing else")
+    ap.add_argument("--design", default=None, choices=["luvavik"],
+                    help="instead of the default benchmark: prefill and decode throughput of this design at layer sizes "
+                         "of real models beside Qwen3 dense at equal size (a JSON line of its own)")
+    ap.add_argument("--design-sizes", default=None, help="with --design: widths to run, e.g. 2048 or 2048,4096")
     args = ap.parse_args()
 
+    if args.design and args.impl != "reference" and args.gpus == 1:
+        return compare_designs(args)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "NeoZedAtlas/Zinfer is a Zig program (needs zig >= 0.15.2); no Zig toolchain exists here and "

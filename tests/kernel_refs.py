@@ -206,6 +206,21 @@ def moe_align(chosen, experts, tile_rows):
     return i32(row_token), i32(row_self), i32(pair_row), i32(tile_expert + [0] * (cap // tile_rows - n_tiles)), i32([n_tiles])
 
 
+MOE_TILE_ROWS_TENSOR = 128
+
+
+def linear_grouped_tensor_ok(weight):
+    return False
+
+
+def gather_rows(x, row_src):
+    out = torch.zeros((row_src.numel(), x.shape[1]), dtype=x.dtype)
+    for r, src in enumerate(row_src.tolist()):
+        if src >= 0:
+            out[r] = x[src]
+    return out
+
+
 def moe_combine(y, x, chosen, weight, pair_row, experts):
     T, H = x.shape
     top = chosen.shape[1]

@@ -23,8 +23,10 @@ import replay_util as ru
 DEV = "cuda:0"
 # float32: the engine against 64-bit arithmetic, both from the same bfloat16-representable weights;
 # relative to a row's largest logit.  bfloat16: products and activations are rounded to 8 bits of
-# mantissa between kernels, over up to eight layer runs.
-TOL = {torch.float32: dict(rtol=5e-5, atol=1e-6), torch.bfloat16: dict(rtol=4e-2, atol=2e-3)}
+# mantissa between kernels, over up to eight layer runs, and the tests' peaky attention (scores spread
+# over tens of units, so that a lost key shows) multiplies the rounding of q and k by that spread.  The
+# float32 runs go through the same kernels and are the sharp test of every index and edge.
+TOL = {torch.float32: dict(rtol=5e-5, atol=1e-6), torch.bfloat16: dict(rtol=8e-2, atol=4e-3)}
 
 
 def plain_logits(cfg, weights, reqs):
@@ -228,17 +230,19 @@ def test_far_keys_page_edges_and_long_memory(tmp_path, dtype):
 
 @gpu
 def test_a_single_far_key_decides(tmp_path):
-    """One key 250 tokens back is made to win the last query's softmax outright (its query and key are
-    scaled up through the embedding of two special tokens); the output then rests on that one value."""
-    cfg = U.config(67, 32, [U.layer(U.attn(2, 8, 8, 8, 16, 4.0), None)])
+    """One key 250 tokens back carries much of the last query's softmax: among all tokens that could stand
+    at position 19, the test takes the one whose presence moves the last position's logits most in the plain
+    model, and requires that move to be large; an engine that lost that key could not match."""
+    cfg = U.config(67, 32, [U.layer(U.attn(2, 8, 8, 8, 16, 1.5), None)])
     weights = U.make_weights(cfg, seed=41)
-    toks = ru.make_requests(cfg["vocab"] - 2, [270], seed=7)["r0"]
-    far, probe = cfg["vocab"] - 2, cfg["vocab"] - 1
-    weights["embed"][probe] = weights["embed"][far]           # the same direction: q . k is then large where they meet
-    toks[19] = far
-    toks[-1] = probe
+    w64 = U.f64(weights)
+    toks = ru.make_requests(cfg["vocab"], [270], seed=7)["r0"]
+    without = toks[:19] + [toks[18]] + toks[20:]
+    lost = plain_logits(cfg, weights, {"r0": without})
+    move = {c: np.abs(P.forward(cfg, w64, toks[:19] + [c] + toks[20:]).numpy()[-1] - lost["r0"][-1]).max()
+            for c in range(cfg["vocab"])}
+    toks[19] = max(move, key=move.get)
     plain = plain_logits(cfg, weights, {"r0": toks})
-    lost = plain_logits(cfg, weights, {"r0": toks[:19] + [toks[18]] + toks[20:]})
     assert np.abs(plain["r0"][-1] - lost["r0"][-1]).max() > 0.05 * np.abs(plain["r0"][-1]).max()     # the far key matters
     for dtype in (torch.float32, torch.bfloat16):
         runner = make_runner(tmp_path, cfg, weights, dtype, DEV, page_size=16, max_tokens=288, max_requests=1)

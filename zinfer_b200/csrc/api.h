@@ -72,6 +72,10 @@ long long zi_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* plan);
 int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K, int ldx, int ldw,
                     int ldo, float* workspace, long long workspace_bytes, int sm_count, int defer_reduce,
                     cudaStream_t stream);
+// Grouped tensor-core product: every 128 rows of x multiply with one group of the stacked weight [groups * N, K].
+int zi_gemm_tcgen05_grouped(void* out, int out_dtype, const void* x, const void* w, int rows, int N, int K, int ldx,
+                            int ldw, int ldo, int groups, const int* tile_group, int relu2, int sm_count,
+                            cudaStream_t stream);
 int zi_gemm_tcgen05_status();
 int zi_gemm_tcgen05_pair_enable(int on);
 
@@ -94,8 +98,10 @@ int zi_latent_prepare(const void* src, int ld, int dtype, int T, int heads, int 
 // Mixture of experts: choice and weights per token, the pairs laid out by expert, the weighted sum.
 int zi_moe_route(int* chosen, float* weight, const float* logits, const float* correction, int T, int NR, int top,
                  int renormalize, cudaStream_t stream);
-int zi_moe_align(const int* chosen, int P, int top, int E, int tile_rows, int* row_token, int* row_self, int* pair_row,
-                 int* tile_expert, int* n_tiles, cudaStream_t stream);
+int zi_moe_align(const int* chosen, int P, int top, int E, int tile_rows, int cap_tiles, int* row_token, int* row_self,
+                 int* pair_row, int* tile_expert, int* n_tiles, cudaStream_t stream);
+int zi_gather_rows(void* out, const void* x, int dtype, const int* row_src, int rows, int width, int ldx,
+                   cudaStream_t stream);
 int zi_moe_combine(void* out, const float* y, const void* x, int dtype, const int* chosen, const float* weight,
                    const int* pair_row, int T, int top, int E, int H, cudaStream_t stream);
 

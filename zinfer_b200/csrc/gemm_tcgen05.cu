@@ -56,6 +56,11 @@ struct GemmArgs {
   int* cand_idx;
   int cand_units;
   int weights_once;          // few tokens: the weight tiles are loaded with the L2 policy "evict first"
+  // Grouped form (tokens on the lanes): the weight is a stack of groups of `group_rows` rows each (the
+  // experts of a mixture), and the tile of token rows a_tile multiplies with group tile_group[a_tile].
+  const int* tile_group;
+  int group_rows;
+  int relu2;                 // plain epilogue: the square of relu before the store
 };
 
 constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2;
@@ -111,6 +116,13 @@ __device__ __forceinline__ void drain_accumulator(const GemmArgs& g, TO* __restr
     }
     const int ncol = min(32, BN - c0);
     const int b0 = b_tile * BN + c0;
+    if (EPI == EPI_PLAIN && g.relu2) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float r = fmaxf(v[j], 0.f);
+        v[j] = r * r;
+      }
+    }
     if (EPI == EPI_ARGMAX) {
       // Floats as unsigned keys in the same order (NaN counts as -inf, -0 as +0; rows past the end
       // get key 0, below every number): one warp-wide maximum and one vote per token, and the
@@ -243,17 +255,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if ((int)blockIdx.x < total_tiles) {
       int a_tile, b_tile, split, kb0, n_kb;
       decode(blockIdx.x, a_tile, b_tile, split, kb0, n_kb);
-      const int pre = min(stages, n_kb);
+      // grouped: which group a tile takes is written by a kernel before this one, so nothing is
+      // requested before the wait for it
+      const int pre = g.tile_group ? 0 : min(stages, n_kb);
       // which: 1 = the weight's tile of k-block i into stage s, 0 = the activations'
       const uint64_t once = l2_policy_evict_first();
+      int group_tile = -1, group_row0 = 0;     // the tile whose group's first weight row is known
       auto issue = [&](int which, int s, int i) {
         uint8_t* dst = smem + (size_t)s * stage_bytes;
         const bool use_a = (which != 0) == (g.a_is_weight != 0);
-        if (which != 0 && g.weights_once)
+        if (which != 0 && g.weights_once) {
           tma_load_2d_hint(dst, &map_a, &full[s], (kb0 + i) * BLOCK_K, a_tile * TILE_A, once);
-        else
+        } else {
+          int b_row = b_tile * BN;
+          if (g.tile_group && !use_a) {
+            if (group_tile != a_tile) {
+              group_tile = a_tile;
+              group_row0 = g.tile_group[a_tile] * g.group_rows;
+            }
+            b_row += group_row0;
+          }
           tma_load_2d(use_a ? dst : dst + A_TILE_BYTES, use_a ? &map_a : &map_b, &full[s], (kb0 + i) * BLOCK_K,
-                      use_a ? a_tile * TILE_A : b_tile * BN);
+                      use_a ? a_tile * TILE_A : b_row);
+        }
       };
       if (lane < pre) {
         mbar_expect_tx(&full[lane], (uint32_t)stage_bytes);
@@ -773,10 +797,13 @@ int launch_single(void* out, const CUtensorMap& map_a, const CUtensorMap& map_b,
 int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtensorMap& map_b, int M, int N, int K,
                 int ldo, const int* plan, float* partial_buf, int* status, int sm_count, int defer_reduce,
                 const char* what, cudaStream_t stream, int epi = EPI_PLAIN, float* cand_val = nullptr,
-                int* cand_idx = nullptr) {
+                int* cand_idx = nullptr, const int* tile_group = nullptr, int relu2 = 0) {
   const int swap = plan[0], BN = plan[1], splits = plan[2];
   const int swiglu = epi == EPI_SWIGLU;
   GemmArgs g;
+  g.tile_group = tile_group;
+  g.group_rows = N;
+  g.relu2 = relu2;
   g.cand_val = cand_val;
   g.cand_idx = cand_idx;
   g.cand_units = swap ? (N + TILE_A - 1) / TILE_A * (TILE_A / 32) : 0;
@@ -807,7 +834,9 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
   const int total_tiles = g.a_tiles * g.b_tiles * g.splits;
   float* partial = g.splits > 1 ? partial_buf : nullptr;
 
-  if (use_pair_kernel(plan, M)) {
+  if (tile_group && (swap || g.splits != 1 || epi != EPI_PLAIN))
+    return zi_refuse("%s: the grouped product runs unsplit with the tokens on the lanes", what);
+  if (!tile_group && use_pair_kernel(plan, M)) {
     ZI_DISPATCH_DTYPE(out_dtype, TO, { return launch_pair<TO>(out, map_a, map_b, g, M, N, K, status, swiglu, what, stream); });
   }
   if (epi == EPI_ARGMAX) {
@@ -852,6 +881,29 @@ extern "C" int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const vo
   if (!status) return zi_refuse("gemm_tcgen05: cannot allocate the status word");
   return launch_gemm(out, out_dtype, map_a, map_b, M, N, K, ldo, plan, workspace, status, sm_count, defer_reduce,
                      "gemm_tcgen05", stream);
+}
+
+// Grouped product for a mixture of experts: row r of x [rows, K] (rows a multiple of 128, already laid
+// out so that every 128 rows belong to one group) multiplies with group tile_group[r / 128] of the
+// stacked weight w [groups * N, K]; out [rows, N].  Which rows are in use is the caller's business:
+// every tile is computed.  relu2: the square of relu in the epilogue.
+extern "C" int zi_gemm_tcgen05_grouped(void* out, int out_dtype, const void* x, const void* w, int rows, int N, int K,
+                                       int ldx, int ldw, int ldo, int groups, const int* tile_group, int relu2,
+                                       int sm_count, cudaStream_t stream) {
+  if (rows <= 0 || N <= 0 || groups <= 0) return 0;
+  if (rows % TILE_A) return zi_refuse("gemm_grouped: %d rows are no whole tiles of %d", rows, TILE_A);
+  if (!tile_group) return zi_refuse("gemm_grouped: no tile groups");
+  if (!zi_gemm_tcgen05_supported(x, w, K, ldx, ldw))
+    return zi_refuse("gemm_grouped: operands must be 16-byte aligned bfloat16 with row pitches in multiples of 8");
+  if ((long long)groups * N > 0x7fffffffLL) return zi_refuse("gemm_grouped: the stacked weight has too many rows");
+  int plan[3] = {0, N >= 256 ? 256 : (N >= 128 ? 128 : round_up_bn(N)), 1};
+  CUtensorMap map_a, map_b;
+  if (!make_map(&map_a, x, rows, K, ldx, TILE_A) || !make_map(&map_b, w, groups * N, K, ldw, plan[1]))
+    return zi_refuse("gemm_grouped: cuTensorMapEncodeTiled failed");
+  int* status = status_word();
+  if (!status) return zi_refuse("gemm_grouped: cannot allocate the status word");
+  return launch_gemm(out, out_dtype, map_a, map_b, rows, N, K, ldo, plan, nullptr, status, sm_count, 0, "gemm_grouped",
+                     stream, EPI_PLAIN, nullptr, nullptr, tile_group, relu2);
 }
 
 // gate_up product with the SwiGLU applied in the epilogue: w is [2I, K] with rows interleaved

@@ -86,9 +86,11 @@ moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, const flo
 //   row_token[r]  token whose input row r multiplies (-1: padding)
 //   row_self[r]   r where the row is in use, else -1
 //   pair_row[p]   row of pair p (-1: an identity expert)
-//   tile_expert[i], *n_tiles
+//   tile_expert[i], *n_tiles     the arrays have cap_tiles tiles (at least P / tile_rows + E); rows and tiles
+//                                beyond the ones in use are marked -1 and expert 0
 __global__ void __launch_bounds__(1024)
-moe_align_kernel(const int* __restrict__ chosen, int P, int top, int E, int tile_rows, int* __restrict__ row_token,
+moe_align_kernel(const int* __restrict__ chosen, int P, int top, int E, int tile_rows, int cap_tiles,
+                 int* __restrict__ row_token,
                  int* __restrict__ row_self, int* __restrict__ pair_row, int* __restrict__ tile_expert,
                  int* __restrict__ n_tiles) {
   pdl_launch_dependents();
@@ -115,9 +117,10 @@ moe_align_kernel(const int* __restrict__ chosen, int P, int top, int E, int tile
     }
     off[E] = o;
     *n_tiles = tiles;
+    for (int i = tiles; i < cap_tiles; ++i) tile_expert[i] = 0;   // tiles not in use still name a group that exists
   }
   __syncthreads();
-  const int rows = off[E];
+  const int rows = cap_tiles * tile_rows;      // all rows the arrays have: a product may walk every tile
   for (int r = threadIdx.x; r < rows; r += blockDim.x) row_token[r] = row_self[r] = -1;
   __syncthreads();
   for (int p = threadIdx.x; p < P; p += blockDim.x) {
@@ -130,6 +133,17 @@ moe_align_kernel(const int* __restrict__ chosen, int P, int top, int E, int tile
     }
     pair_row[p] = r;
   }
+}
+
+// out[r] = x[row_src[r]], or zeros where row_src[r] is -1: the tokens' rows in the order of the pairs.
+template <typename T>
+__global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ x, const int* __restrict__ row_src,
+                                   int width, int ldx) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x, src = row_src[r];
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    out[(size_t)r * width + c] = src >= 0 ? x[(size_t)src * ldx + c] : from_f32<T>(0.f);
 }
 
 // out[t] = sum_k weight[t,k] * (expert output of pair (t,k), or x[t] for an identity expert), k ascending.
@@ -164,14 +178,23 @@ extern "C" int zi_moe_route(int* chosen, float* weight, const float* logits, con
   return zi_check_launch("moe_route");
 }
 
-extern "C" int zi_moe_align(const int* chosen, int P, int top, int E, int tile_rows, int* row_token, int* row_self,
-                            int* pair_row, int* tile_expert, int* n_tiles, cudaStream_t stream) {
+extern "C" int zi_moe_align(const int* chosen, int P, int top, int E, int tile_rows, int cap_tiles, int* row_token,
+                            int* row_self, int* pair_row, int* tile_expert, int* n_tiles, cudaStream_t stream) {
   if (P <= 0) return 0;
+  if (cap_tiles < (P + tile_rows - 1) / tile_rows + E) return zi_refuse("moe_align: %d tiles cannot hold %d pairs of %d experts", cap_tiles, P, E);
   const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
   if (smem > 48 * 1024) return zi_refuse("moe_align: %d experts are more than this kernel holds", E);
-  zi_launch(moe_align_kernel, dim3(1), dim3(1024), smem, stream, chosen, P, top, E, tile_rows, row_token, row_self,
-            pair_row, tile_expert, n_tiles);
+  zi_launch(moe_align_kernel, dim3(1), dim3(1024), smem, stream, chosen, P, top, E, tile_rows, cap_tiles, row_token,
+            row_self, pair_row, tile_expert, n_tiles);
   return zi_check_launch("moe_align");
+}
+
+extern "C" int zi_gather_rows(void* out, const void* x, int dtype, const int* row_src, int rows, int width, int ldx,
+                              cudaStream_t stream) {
+  if (rows <= 0 || width <= 0) return 0;
+  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(gather_rows_kernel<TT>, dim3(rows), dim3(256), 0, stream, (TT*)out, (const TT*)x,
+                                         row_src, width, ldx));
+  return zi_check_launch("gather_rows");
 }
 
 extern "C" int zi_moe_combine(void* out, const float* y, const void* x, int dtype, const int* chosen,

@@ -505,7 +505,9 @@ def linear_grouped(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row
     _need(rows % tile_rows == 0 and row_src.numel() >= rows, "linear_grouped: whole tiles of rows")
     for t, name in ((row_src, "row_src"), (tile_group, "tile_group"), (n_tiles, "n_tiles")):
         _i32(t, name)
-    with _prof.region(f"linear (CUDA cores, grouped) N={N} K={K}"):
+    pairs = max(1, rows - G * tile_rows)       # about as many rows are in use
+    with _prof.region(f"linear (CUDA cores, grouped) N={N} K={K}", lambda: _nb(weight, out) + pairs * K * x.element_size(),
+                      2 * pairs * N * K):
         _check(lib().zi_gemm_simt_general(
             _ptr(out), _tag(out), _ptr(x), _tag(x), _ptr(weight), _tag(weight), rows, N, K, x.stride(0), K, out.stride(0),
             1, _ll(0), _ll(0), _ll(0), None, _ll(0), _ptr(row_src), _ptr(tile_group), _ptr(n_tiles), _ll(N * K),
@@ -531,7 +533,7 @@ def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int
     return chosen, weight
 
 
-MOE_TILE_ROWS_SMALL, MOE_TILE_ROWS = 16, 64
+MOE_TILE_ROWS_SMALL, MOE_TILE_ROWS, MOE_TILE_ROWS_TENSOR = 16, 64, 128
 
 
 def moe_align(chosen: torch.Tensor, experts: int, tile_rows: int):
@@ -548,9 +550,46 @@ def moe_align(chosen: torch.Tensor, experts: int, tile_rows: int):
     row_token, row_self, pair_row = buf[:n], buf[n:2 * n], buf[2 * n:2 * n + P]
     tile_expert, n_tiles = buf[2 * n + P:2 * n + P + cap_tiles], buf[2 * n + P + cap_tiles:]
     with _prof.region("moe align", lambda: _nb(chosen) + 3 * P * 4):
-        _check(lib().zi_moe_align(_ptr(_i32(chosen, "chosen")), P, top, experts, tile_rows, _ptr(row_token), _ptr(row_self),
-                                  _ptr(pair_row), _ptr(tile_expert), _ptr(n_tiles), _stream()), "moe_align")
+        _check(lib().zi_moe_align(_ptr(_i32(chosen, "chosen")), P, top, experts, tile_rows, cap_tiles, _ptr(row_token),
+                                  _ptr(row_self), _ptr(pair_row), _ptr(tile_expert), _ptr(n_tiles), _stream()), "moe_align")
     return row_token, row_self, pair_row, tile_expert, n_tiles
+
+
+def gather_rows(x: torch.Tensor, row_src: torch.Tensor) -> torch.Tensor:
+    """``out[r] = x[row_src[r]]`` (zeros where ``row_src[r]`` is -1): rows of ``x`` in another order."""
+    rows, W = row_src.numel(), x.shape[1]
+    _need(x.stride(1) == 1, "gather_rows: dense rows")
+    out = torch.empty((rows, W), dtype=x.dtype, device=x.device)
+    with _prof.region("gather rows", lambda: 2 * _nb(out)):
+        _check(lib().zi_gather_rows(_ptr(out), _ptr(x), _tag(x), _ptr(_i32(row_src, "row_src")), rows, W, x.stride(0),
+                                    _stream()), "gather_rows")
+    return out
+
+
+def linear_grouped_tensor_ok(weight: torch.Tensor) -> bool:
+    """Whether :func:`linear_grouped_tensor` takes this stacked weight [G, N, K] (bfloat16 that meets TMA's
+    alignment rules; its other operand is a fresh contiguous bfloat16 tensor with K columns)."""
+    return bool(GEMM_BACKEND != "simt" and weight.dtype == torch.bfloat16 and weight.is_contiguous()
+                and lib().zi_gemm_tcgen05_supported(_ptr(weight), _ptr(weight), weight.shape[2], weight.shape[2],
+                                                    weight.shape[2]))
+
+
+def linear_grouped_tensor(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor,
+                          relu2: bool = False, pairs: int = 0) -> torch.Tensor:
+    """The grouped product on the tcgen05 kernel: every 128 rows of ``x`` [rows, K] (bfloat16, laid out by
+    group already) multiply with group ``tile_group[r // 128]`` of ``weight`` [G, N, K]; ``out`` [rows, N].
+    Every tile is computed, also those past the rows in use (their results are never read).  ``pairs``:
+    rows in use, for the profiler's count of useful operations."""
+    G, N, K = weight.shape
+    rows = x.shape[0]
+    _need(out.shape == (rows, N) and out.stride(1) == 1 and rows % MOE_TILE_ROWS_TENSOR == 0, "linear_grouped_tensor: shapes")
+    _need(tile_group.numel() >= rows // MOE_TILE_ROWS_TENSOR, "linear_grouped_tensor: a group per tile")
+    with _prof.region(f"linear (grouped, tcgen05) N={N} K={K}", lambda: _nb(weight, out) + rows * K * 2,
+                      2 * (pairs or rows) * N * K):
+        _check(lib().zi_gemm_tcgen05_grouped(_ptr(out), _tag(out), _ptr(x), _ptr(weight), rows, N, K, x.stride(0), K,
+                                             out.stride(0), G, _ptr(_i32(tile_group, "tile_group")), 1 if relu2 else 0,
+                                             _sm_count(x.device), _stream()), "linear_grouped_tensor")
+    return out
 
 
 def moe_combine(y: torch.Tensor, x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, pair_row: torch.Tensor,

@@ -38,6 +38,8 @@ class RoutedExperts(FeedForward):
         if not 1 <= self.top <= self.outputs:
             raise ValueError(f"{self.top} of {self.outputs} router outputs cannot be chosen")
         self.expert_names = params.get("expert_names", "e{}.")     # prefix of expert i's tensors
+        # from this many (token, expert) pairs in a step the products go to the tensor cores (bfloat16)
+        self.tensor_core_pairs = int(params.get("tensor_core_pairs", 64))
 
     def tensor_specs(self):
         specs = {"router": TensorSpec((self.outputs, self.hidden))}
@@ -64,7 +66,21 @@ class RoutedExperts(FeedForward):
         T = x.shape[0]
         logits = ops.linear_cuda_cores(x, self.w_router, out_dtype=torch.float32)     # 32-bit multiply-adds
         chosen, weight = ops.moe_route(logits, self.correction, self.top, self.renormalize)
-        tile = ops.MOE_TILE_ROWS if T * self.top > 16 * max(self.experts, 1) else ops.MOE_TILE_ROWS_SMALL
+        pairs = T * self.top
+        if pairs >= self.tensor_core_pairs and x.dtype == torch.bfloat16 and self.experts > 0 \
+                and ops.linear_grouped_tensor_ok(self.w_up) and ops.linear_grouped_tensor_ok(self.w_down):
+            # a prompt's portion in bfloat16: the pairs' rows are gathered by expert into tiles of 128 and
+            # both products run on the tensor cores
+            tile = ops.MOE_TILE_ROWS_TENSOR
+            row_token, row_self, pair_row, tile_expert, n_tiles = ops.moe_align(chosen, self.experts, tile)
+            rows = row_token.numel()
+            xs = ops.gather_rows(x, row_token)
+            mid = torch.empty((rows, self.inter), dtype=self.ctx.dtype, device=x.device)
+            ops.linear_grouped_tensor(xs, self.w_up, mid, tile_expert, relu2=True, pairs=pairs)
+            y = torch.empty((rows, self.hidden), dtype=torch.float32, device=x.device)
+            ops.linear_grouped_tensor(mid, self.w_down, y, tile_expert, pairs=pairs)
+            return ops.moe_combine(y, x, chosen, weight, pair_row, self.experts)
+        tile = ops.MOE_TILE_ROWS if pairs > 16 * max(self.experts, 1) else ops.MOE_TILE_ROWS_SMALL
         row_token, row_self, pair_row, tile_expert, n_tiles = ops.moe_align(chosen, self.experts, tile)
         rows = row_token.numel()
         mid = torch.empty((rows, self.inter), dtype=self.ctx.dtype, device=x.device)
