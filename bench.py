@@ -171,7 +171,7 @@ def compare_designs(args) -> int:
     def measure(name, cfg, vocab):
         engine = Engine(config=cfg, random_weights_seed=7, dtype="bfloat16", device="cuda:0", page_size=16,
                         kv_cache_tokens=batch * (context + steps + warmup + 64) + tokens + 64,
-                        max_batched_tokens=tokens, max_requests=batch, max_model_len=8192)
+                        max_batched_tokens=tokens, max_requests=batch + 1, max_model_len=8192)
         runner = engine.runner
         rand = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
         prompt = rand(tokens)

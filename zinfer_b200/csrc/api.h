@@ -86,14 +86,22 @@ int zi_paged_attention(void* out, int out_stride, const void* q, int q_stride, i
                        int d, int page_size, int window, float scale, cudaStream_t stream);
 
 // The same with dv <= d value columns read from rows of v_row elements (values may lie in the key rows).
+// skip_from > 0: requests that bring that many tokens or more are left out (another kernel serves them).
 int zi_paged_attention_v(void* out, int out_stride, const void* q, int q_stride, int dtype, const void* kcache,
                          const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
                          const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
-                         int d, int dv, int v_row, int page_size, int window, float scale, cudaStream_t stream);
+                         int d, int dv, int v_row, int page_size, int window, float scale, int skip_from,
+                         cudaStream_t stream);
 // Latent attention: the cached row [normed latent | rotated key part] and the rotated query part of a token.
 int zi_latent_prepare(const void* src, int ld, int dtype, int T, int heads, int dim, int rd, int rank, int rot_dims,
                       const float* cw, float eps, const float* cos_t, const float* sin_t, int n_table_pos,
                       const int* positions, void* q_eff, void* cache, const int* slots, int write_cache,
+                      cudaStream_t stream);
+// For a prompt's portion on the tensor cores: a request's cached rows gathered ([kv_pad, D], and the first `rank`
+// columns transposed [rank, kv_pad]), and the causal softmax of the portion's score matrix.
+int zi_latent_gather(void* keys, void* values_t, const void* cache, int dtype, const int* block_table, int page_size,
+                     int kv_len, int kv_pad, int D, int rank, cudaStream_t stream);
+int zi_causal_softmax(void* P, const float* S, int dtype, long long rows, int heads, int ctx, int kv_pad, float scale,
                       cudaStream_t stream);
 // Mixture of experts: choice and weights per token, the pairs laid out by expert, the weighted sum.
 int zi_moe_route(int* chosen, float* weight, const float* logits, const float* correction, int T, int NR, int top,

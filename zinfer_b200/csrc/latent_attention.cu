@@ -71,7 +71,91 @@ latent_prepare_kernel(const T* __restrict__ src, int ld, int heads, int dim, int
     out[rank + i] = from_f32<T>(v);
   }
 }
+
+// A request's cached rows, gathered from its pages for the tensor-core products of a prompt's portion:
+// keys[j, :] = row j (all D columns; rows kv_len .. kv_pad-1 are zero) and values_t[r, j] = row j's
+// column r for r < rank (the latent part, transposed: the second product's weight-side operand).
+// One block takes 32 keys.
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_gather_kernel(T* __restrict__ keys, T* __restrict__ values_t, const T* __restrict__ cache,
+                     const int* __restrict__ block_table, int page_size, int kv_len, int kv_pad, int D, int rank) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ unsigned char raw[];
+  T* tile = reinterpret_cast<T*>(raw);           // [32][D + 2]
+  const int j0 = blockIdx.x * 32, pitch = D + 2;
+  for (int e = threadIdx.x; e < 32 * D; e += blockDim.x) {
+    const int kk = e / D, c = e - kk * D, j = j0 + kk;
+    T v = from_f32<T>(0.f);
+    if (j < kv_len) {
+      const int page = block_table[j / page_size];
+      if (page >= 0) v = cache[((size_t)page * page_size + (j % page_size)) * D + c];
+    }
+    tile[kk * pitch + c] = v;
+    if (j < kv_pad) keys[(size_t)j * D + c] = v;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < 32 * rank; e += blockDim.x) {
+    const int r = e / 32, kk = e - r * 32, j = j0 + kk;
+    if (j < kv_pad) values_t[(size_t)r * kv_pad + j] = tile[kk * pitch + r];
+  }
+}
+
+// Causal softmax over a portion's scores: row (t, h) of S [rows, kv_pad] (32-bit) belongs to the query at
+// position ctx + t and sees keys 0 .. ctx + t; P[row, j] = exp(scale * (S - max)) / sum there, 0 beyond
+// (also in the padding columns), written in the activations' type for the second product.
+template <typename T>
+__global__ void __launch_bounds__(256)
+causal_softmax_kernel(T* __restrict__ P, const float* __restrict__ S, int heads, int ctx, int kv_pad, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  __shared__ float red[8];
+  const size_t row = blockIdx.x;
+  const int visible = ctx + (int)(row / heads) + 1;
+  const float* s = S + row * kv_pad;
+  T* p = P + row * kv_pad;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float m = -INFINITY;
+  for (int j = threadIdx.x; j < visible; j += blockDim.x) m = fmaxf(m, s[j]);
+  m = warp_max(m);
+  if (lane == 0) red[warp] = m;
+  __syncthreads();
+  m = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+  float sum = 0.f;
+  for (int j = threadIdx.x; j < visible; j += blockDim.x) sum += expf(scale * (s[j] - m));
+  const float inv = 1.0f / block_sum(sum, scratch);
+  for (int j = threadIdx.x; j < kv_pad; j += blockDim.x)
+    p[j] = from_f32<T>(j < visible ? expf(scale * (s[j] - m)) * inv : 0.f);
+}
 }  // namespace
+
+extern "C" int zi_latent_gather(void* keys, void* values_t, const void* cache, int dtype, const int* block_table,
+                                int page_size, int kv_len, int kv_pad, int D, int rank, cudaStream_t stream) {
+  if (kv_pad <= 0) return 0;
+  if (rank > D || kv_len > kv_pad) return zi_refuse("latent_gather: rank %d of %d columns, %d of %d keys", rank, D, kv_len, kv_pad);
+  const size_t smem = (size_t)32 * (D + 2) * (dtype == ZI_F32 ? 4 : 2);
+  ZI_DISPATCH_DTYPE(dtype, TT, {
+    auto kern = latent_gather_kernel<TT>;
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return zi_refuse("latent_gather: cannot get %zu bytes of shared memory", smem);
+    zi_launch(kern, dim3((kv_pad + 31) / 32), dim3(256), smem, stream, (TT*)keys, (TT*)values_t, (const TT*)cache,
+              block_table, page_size, kv_len, kv_pad, D, rank);
+  });
+  return zi_check_launch("latent_gather");
+}
+
+extern "C" int zi_causal_softmax(void* P, const float* S, int dtype, long long rows, int heads, int ctx, int kv_pad,
+                                 float scale, cudaStream_t stream) {
+  if (rows <= 0 || kv_pad <= 0) return 0;
+  if (rows > 0x7fffffffLL) return zi_refuse("causal_softmax: too many rows");
+  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(causal_softmax_kernel<TT>, dim3((unsigned)rows), dim3(256), 0, stream, (TT*)P, S,
+                                         heads, ctx, kv_pad, scale));
+  return zi_check_launch("causal_softmax");
+}
 
 extern "C" int zi_latent_prepare(const void* src, int ld, int dtype, int T, int heads, int dim, int rd, int rank,
                                  int rot_dims, const float* cw, float eps, const float* cos_t, const float* sin_t,

@@ -672,23 +672,68 @@ def latent_prepare(proj: torch.Tensor, heads: int, dim: int, rot_dim: int, rank:
                                        1 if cache is not None else 0, _stream()), "latent_prepare")
 
 
+# A request that brings this many tokens or more in a bfloat16 step has its latent attention on the
+# tensor cores (two products around a causal softmax); fewer go to the exact kernel.
+LATENT_TENSOR_MIN_TOKENS = 32
+
+
 def latent_attention(q_eff: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, step, heads: int, rank: int,
                      page_size: int, window: Optional[int], scale: float) -> torch.Tensor:
     """Causal softmax attention of ``q_eff`` [T, heads * D] over the latent rows of each request's pages
     (``cache`` [pages, 1, page_size, D]): scores over all D columns, values the first ``rank`` columns.
-    Returns [T, heads * rank].  32-bit arithmetic on the CUDA cores."""
+    Returns [T, heads * rank].
+
+    In float32, and for requests that bring few tokens, the exact kernel on the CUDA cores.  In bfloat16 a
+    request's longer portion runs as two tcgen05 products: its cached rows are gathered from the pages (once
+    as they are, once with the latent part transposed), S = Q rows^T in 32-bit, a causal softmax in 32-bit
+    that writes P in bfloat16, then P times the latent part.  The scores of a portion against all its keys
+    pass through memory; a portion of 2,048 tokens of 16 heads against 2,048 keys holds 268 MB for that."""
     T = q_eff.shape[0]
     D = cache.shape[-1]
     _need(q_eff.shape[1] == heads * D and q_eff.is_contiguous() and cache.is_contiguous() and cache.dtype == q_eff.dtype,
           "latent_attention: shapes")
     out = torch.empty((T, heads * rank), dtype=q_eff.dtype, device=q_eff.device)
+    skip_from = 0
+    if (q_eff.dtype == torch.bfloat16 and not window and GEMM_BACKEND != "simt" and ATTENTION_BACKEND != "generic"
+            and D % 8 == 0 and rank % 8 == 0 and getattr(step, "q_lens", None)
+            and max(step.q_lens) >= LATENT_TENSOR_MIN_TOKENS):
+        skip_from = LATENT_TENSOR_MIN_TOKENS
+        t0 = 0
+        for s, (n, ctx) in enumerate(zip(step.q_lens, step.ctx_lens)):
+            if n >= skip_from:
+                _latent_attention_portion(q_eff[t0:t0 + n], out[t0:t0 + n], cache, block_tables[s], heads, rank, D,
+                                          page_size, ctx, scale)
+            t0 += n
+        if all(n >= skip_from for n in step.q_lens):
+            return out
     with _prof.region("latent attention (exact, CUDA cores)"):
         _check(lib().zi_paged_attention_v(
             _ptr(out), out.stride(0), _ptr(q_eff), q_eff.stride(0), _tag(q_eff), _ptr(cache), _ptr(cache),
             _ptr(_i32(block_tables, "block_tables")), block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens),
             _ptr(step.tile_seq), _ptr(step.tile_q0), step.tile_seq.shape[0], heads, 1, D, rank, D, page_size,
-            int(window or 0), ctypes.c_float(scale), _stream()), "latent_attention")
+            int(window or 0), ctypes.c_float(scale), skip_from, _stream()), "latent_attention")
     return out
+
+
+def _latent_attention_portion(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                              heads: int, rank: int, D: int, page_size: int, ctx: int, scale: float) -> None:
+    """One request's portion of ``n`` tokens that follow ``ctx`` cached ones, on the tensor cores."""
+    n = q.shape[0]
+    kv = ctx + n
+    kv_pad = -(-kv // 8) * 8                      # rows of 16 bytes for the second product
+    rows = n * heads
+    dev = q.device
+    keys = torch.empty((kv_pad, D), dtype=q.dtype, device=dev)
+    values_t = torch.empty((rank, kv_pad), dtype=q.dtype, device=dev)
+    with _prof.region("latent attention: gather rows", lambda: 2 * _nb(keys) + _nb(values_t)):
+        _check(lib().zi_latent_gather(_ptr(keys), _ptr(values_t), _ptr(cache), _tag(cache), _ptr(_i32(block_table, "block_table")),
+                                      page_size, kv, kv_pad, D, rank, _stream()), "latent_gather")
+    scores = linear(q.view(rows, D), keys, out_dtype=torch.float32)
+    probs = torch.empty((rows, kv_pad), dtype=q.dtype, device=dev)
+    with _prof.region("latent attention: causal softmax", lambda: _nb(scores, probs)):
+        _check(lib().zi_causal_softmax(_ptr(probs), _ptr(scores), _tag(probs), ctypes.c_longlong(rows), heads, ctx, kv_pad,
+                                       ctypes.c_float(scale), _stream()), "causal_softmax")
+    linear(probs, values_t, out=out.view(rows, rank))
 
 
 # ----------------------------------------------------------------------- attention
