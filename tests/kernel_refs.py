@@ -131,7 +131,7 @@ def qk_norm_rope_store(qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weigh
     return qkv
 
 
-def linear(x, weight, out_dtype=None, out=None, allow_partials=False):
+def linear(x, weight, out_dtype=None, out=None, allow_partials=False, fresh_weight=False):
     y = x.to(torch.float32) @ weight.to(torch.float32).T
     if out is not None:
         out.copy_(y)
@@ -276,6 +276,15 @@ def rglru_scan(u, gates, block_width, r_bias, i_bias, lam, decay_scale, y, y_bia
     return (out * gelu_tanh(y.to(torch.float32) + y_bias)).to(y.dtype)
 
 
+def rglru_decode(yx, y_bias, x_bias, kernel, bias, w_gates, r_bias, i_bias, lam, decay_scale, state, step):
+    n, C = yx.shape[0], yx.shape[1] // 2
+    B, _, bw = w_gates.shape
+    y, x = yx[:, :C], yx[:, C:]
+    u = causal_conv(x, x_bias, kernel, bias, state, step)
+    gates = torch.einsum("tbi,boi->tbo", u.view(n, B, bw), w_gates.to(torch.float32)).contiguous()
+    return rglru_scan(u, gates, bw, r_bias, i_bias, lam, decay_scale, y, y_bias, x, x_bias, state, step)
+
+
 # ----------------------------------------------------------------- latent attention
 def _rotate_first(v, cos, sin, rot_dims):
     half = rot_dims // 2
@@ -301,6 +310,10 @@ def latent_prepare(proj, heads, dim, rot_dim, rank, rot_dims, c_weight, eps, cos
         slot = int(slots[t])
         if slot >= 0:
             cache[slot // page_size, 0, slot % page_size] = row[t]
+
+
+def latent_decode_splits(n_dec, head_groups, sm_count, max_kv_len, fixed=False):
+    return 1
 
 
 def latent_attention(q_eff, cache, block_tables, step, heads, rank, page_size, window, scale):

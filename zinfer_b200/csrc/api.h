@@ -67,6 +67,12 @@ int zi_rglru_scan(void* out, int ldo, const float* u, const float* gates, int bl
                   const void* x, int ldx, const float* xb, int dtype, float* state, int C, int taps, const int* cu_q,
                   const int* state_slots, int n_seqs, cudaStream_t stream);
 
+// One token per request: convolution, gates, recurrence and gated output in one kernel.  yx rows: y branch, x branch.
+int zi_rglru_decode(void* out, int ldo, const void* yx, int ld, int dtype, const float* yb, const float* xb,
+                    const float* kern, const float* cb, const void* wg, int wg_dtype, int block_width, const float* rb,
+                    const float* ib, const float* lam, float decay_scale, float* state, int C, int taps,
+                    const int* state_slots, int n_seqs, cudaStream_t stream);
+
 int zi_gemm_tcgen05_supported(const void* x, const void* w, int K, int ldx, int ldw);
 long long zi_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* plan);
 int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K, int ldx, int ldw,
@@ -86,12 +92,13 @@ int zi_paged_attention(void* out, int out_stride, const void* q, int q_stride, i
                        int d, int page_size, int window, float scale, cudaStream_t stream);
 
 // The same with dv <= d value columns read from rows of v_row elements (values may lie in the key rows).
-// skip_from > 0: requests that bring that many tokens or more are left out (another kernel serves them).
+// skip_from > 0: requests that bring that many tokens or more are left out (another kernel serves them);
+// skip_single: so are requests that bring exactly one.
 int zi_paged_attention_v(void* out, int out_stride, const void* q, int q_stride, int dtype, const void* kcache,
                          const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
                          const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
                          int d, int dv, int v_row, int page_size, int window, float scale, int skip_from,
-                         cudaStream_t stream);
+                         int skip_single, cudaStream_t stream);
 // Latent attention: the cached row [normed latent | rotated key part] and the rotated query part of a token.
 int zi_latent_prepare(const void* src, int ld, int dtype, int T, int heads, int dim, int rd, int rank, int rot_dims,
                       const float* cw, float eps, const float* cos_t, const float* sin_t, int n_table_pos,
@@ -103,6 +110,11 @@ int zi_latent_gather(void* keys, void* values_t, const void* cache, int dtype, c
                      int kv_len, int kv_pad, int D, int rank, cudaStream_t stream);
 int zi_causal_softmax(void* P, const float* S, int dtype, long long rows, int heads, int ctx, int kv_pad, float scale,
                       cudaStream_t stream);
+// Requests that bring one token: split-key attention over the latent rows, all heads of a group per fetched row.
+long long zi_latent_decode_workspace_floats(int n_dec, int heads, int rank, int splits);
+int zi_latent_decode(void* out, int out_stride, float* work, const void* q, int q_stride, int dtype, const void* cache,
+                     const int* block_tables, int bt_stride, const int* cu_q, const int* kv_lens, const int* dec_seq,
+                     int n_dec, int heads, int D, int rank, int page_size, float scale, int splits, cudaStream_t stream);
 // Mixture of experts: choice and weights per token, the pairs laid out by expert, the weighted sum.
 int zi_moe_route(int* chosen, float* weight, const float* logits, const float* correction, int T, int NR, int top,
                  int renormalize, cudaStream_t stream);

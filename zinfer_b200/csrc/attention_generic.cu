@@ -25,7 +25,7 @@ paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict_
                        const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_q,
                        const int* __restrict__ kv_lens, const int* __restrict__ tile_seq,
                        const int* __restrict__ tile_q0, int nq, int nkv, int d, int page_size, int window,
-                       float scale, int dv, int v_row, int skip_from) {
+                       float scale, int dv, int v_row, int skip_from, int skip_single) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float smem[];
@@ -39,7 +39,7 @@ paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict_
   const int tok0 = cu_q[seq], qlen = cu_q[seq + 1] - tok0, kvlen = kv_lens[seq];
   const int ctx = kvlen - qlen;  // tokens of this request already in the cache before this step
   const int nqv = min(BQ, qlen - q0);
-  if (nqv <= 0 || (skip_from > 0 && qlen >= skip_from)) return;
+  if (nqv <= 0 || (skip_from > 0 && qlen >= skip_from) || (skip_single && qlen == 1)) return;
   const int first_pos = ctx + q0, last_pos = first_pos + nqv - 1;
   const int kv_begin = window > 0 ? max(0, first_pos - window + 1) : 0;
   const int kv_end = last_pos + 1;
@@ -143,14 +143,14 @@ extern "C" int zi_paged_attention(void* out, int out_stride, const void* q, int 
                                   int n_tiles, int nq, int nkv, int d, int page_size, int window, float scale,
                                   cudaStream_t stream) {
   return zi_paged_attention_v(out, out_stride, q, q_stride, dtype, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
-                              tile_seq, tile_q0, n_tiles, nq, nkv, d, d, d, page_size, window, scale, 0, stream);
+                              tile_seq, tile_q0, n_tiles, nq, nkv, d, d, d, page_size, window, scale, 0, 0, stream);
 }
 
 extern "C" int zi_paged_attention_v(void* out, int out_stride, const void* q, int q_stride, int dtype,
                                     const void* kcache, const void* vcache, const int* block_tables, int bt_stride,
                                     const int* cu_q, const int* kv_lens, const int* tile_seq, const int* tile_q0,
                                     int n_tiles, int nq, int nkv, int d, int dv, int v_row, int page_size, int window,
-                                    float scale, int skip_from, cudaStream_t stream) {
+                                    float scale, int skip_from, int skip_single, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   constexpr int WIDE = 20;   // value columns up to 640 (latent caches); 8 serves every ordinary head size
   if (d <= 0 || d > 32 * WIDE) return zi_refuse("paged_attention: head_dim %d is outside 1..%d", d, 32 * WIDE);
@@ -168,7 +168,7 @@ extern "C" int zi_paged_attention_v(void* out, int out_stride, const void* q, in
     }                                                                                                              \
     zi_launch(kern, dim3(grid), dim3(THREADS), smem, stream, (TT*)out, out_stride, (const TT*)q, q_stride,         \
               (const TT*)kcache, (const TT*)vcache, block_tables, bt_stride, cu_q, kv_lens, tile_seq, tile_q0, nq, \
-              nkv, d, page_size, window, scale, dv, v_row, skip_from);                                             \
+              nkv, d, page_size, window, scale, dv, v_row, skip_from, skip_single);                                \
   } while (0)
   ZI_DISPATCH_DTYPE(dtype, TT, {
     if (dv <= 256) ZI_LAUNCH_ATTN(8);

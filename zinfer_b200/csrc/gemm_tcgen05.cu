@@ -61,6 +61,8 @@ struct GemmArgs {
   const int* tile_group;
   int group_rows;
   int relu2;                 // plain epilogue: the square of relu before the store
+  int late_weights;          // the weight-side operand is written by a kernel of this step: nothing is
+                             // requested before the wait for the kernels before this one
 };
 
 constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2;
@@ -257,7 +259,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       decode(blockIdx.x, a_tile, b_tile, split, kb0, n_kb);
       // grouped: which group a tile takes is written by a kernel before this one, so nothing is
       // requested before the wait for it
-      const int pre = g.tile_group ? 0 : min(stages, n_kb);
+      const int pre = (g.tile_group || g.late_weights) ? 0 : min(stages, n_kb);
       // which: 1 = the weight's tile of k-block i into stage s, 0 = the activations'
       const uint64_t once = l2_policy_evict_first();
       int group_tile = -1, group_row0 = 0;     // the tile whose group's first weight row is known
@@ -804,6 +806,8 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
   g.tile_group = tile_group;
   g.group_rows = N;
   g.relu2 = relu2;
+  g.late_weights = (defer_reduce >> 1) & 1;
+  defer_reduce &= 1;
   g.cand_val = cand_val;
   g.cand_idx = cand_idx;
   g.cand_units = swap ? (N + TILE_A - 1) / TILE_A * (TILE_A / 32) : 0;
@@ -860,8 +864,10 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
 }
 }  // namespace
 
-// With `defer_reduce` and a split product, the partial sums are left in `workspace` as
-// [splits, M, N] floats for a consumer that adds them itself, and `out` is not written.
+// With `defer_reduce` (bit 0) and a split product, the partial sums are left in `workspace` as
+// [splits, M, N] floats for a consumer that adds them itself, and `out` is not written.  Bit 1 of
+// `defer_reduce`: w is not a weight but written by an earlier kernel of the step; its tiles are then
+// not requested ahead of the wait for those kernels.
 extern "C" int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K, int ldx,
                                int ldw, int ldo, float* workspace, long long workspace_bytes, int sm_count,
                                int defer_reduce, cudaStream_t stream) {

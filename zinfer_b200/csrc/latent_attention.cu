@@ -74,7 +74,8 @@ latent_prepare_kernel(const T* __restrict__ src, int ld, int heads, int dim, int
 
 // A request's cached rows, gathered from its pages for the tensor-core products of a prompt's portion:
 // keys[j, :] = row j (all D columns; rows kv_len .. kv_pad-1 are zero) and values_t[r, j] = row j's
-// column r for r < rank (the latent part, transposed: the second product's weight-side operand).
+// column r for r < rank (the latent part, transposed: the second product's weight-side operand), held
+// twice side by side ([rank, 2 kv_pad]) because the softmax weights come as a high and a low part.
 // One block takes 32 keys.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -98,13 +99,18 @@ latent_gather_kernel(T* __restrict__ keys, T* __restrict__ values_t, const T* __
   __syncthreads();
   for (int e = threadIdx.x; e < 32 * rank; e += blockDim.x) {
     const int r = e / 32, kk = e - r * 32, j = j0 + kk;
-    if (j < kv_pad) values_t[(size_t)r * kv_pad + j] = tile[kk * pitch + r];
+    if (j < kv_pad) {
+      values_t[(size_t)r * 2 * kv_pad + j] = tile[kk * pitch + r];
+      values_t[(size_t)r * 2 * kv_pad + kv_pad + j] = tile[kk * pitch + r];
+    }
   }
 }
 
 // Causal softmax over a portion's scores: row (t, h) of S [rows, kv_pad] (32-bit) belongs to the query at
-// position ctx + t and sees keys 0 .. ctx + t; P[row, j] = exp(scale * (S - max)) / sum there, 0 beyond
-// (also in the padding columns), written in the activations' type for the second product.
+// position ctx + t and sees keys 0 .. ctx + t; p = exp(scale * (S - max)) / sum there, 0 beyond (also in
+// the padding columns).  The weights are 32-bit; for the second product each is written as two values of
+// the activations' type, P[row, j] = round(p) and P[row, kv_pad + j] = round(p - P[row, j]), whose sum
+// carries 16 bits of p, so that the product loses nothing a 32-bit weight would have kept.
 template <typename T>
 __global__ void __launch_bounds__(256)
 causal_softmax_kernel(T* __restrict__ P, const float* __restrict__ S, int heads, int ctx, int kv_pad, float scale) {
@@ -115,7 +121,7 @@ causal_softmax_kernel(T* __restrict__ P, const float* __restrict__ S, int heads,
   const size_t row = blockIdx.x;
   const int visible = ctx + (int)(row / heads) + 1;
   const float* s = S + row * kv_pad;
-  T* p = P + row * kv_pad;
+  T* p = P + row * 2 * kv_pad;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float m = -INFINITY;
   for (int j = threadIdx.x; j < visible; j += blockDim.x) m = fmaxf(m, s[j]);
@@ -128,10 +134,203 @@ causal_softmax_kernel(T* __restrict__ P, const float* __restrict__ S, int heads,
   float sum = 0.f;
   for (int j = threadIdx.x; j < visible; j += blockDim.x) sum += expf(scale * (s[j] - m));
   const float inv = 1.0f / block_sum(sum, scratch);
-  for (int j = threadIdx.x; j < kv_pad; j += blockDim.x)
-    p[j] = from_f32<T>(j < visible ? expf(scale * (s[j] - m)) * inv : 0.f);
+  for (int j = threadIdx.x; j < kv_pad; j += blockDim.x) {
+    const float w = j < visible ? expf(scale * (s[j] - m)) * inv : 0.f;
+    const T hi = from_f32<T>(w);
+    p[j] = hi;
+    p[kv_pad + j] = from_f32<T>(w - to_f32(hi));
+  }
+}
+
+// ------------------------------------------------------------ single tokens: split-key decode
+// A request that brings one token: its `heads` query rows [D] against its kv_len cached rows, which
+// every head shares.  Block (key split, request, group of 16 heads): 256 threads walk the split's keys
+// in tiles of 32 rows held in shared memory as 32-bit values; a row is fetched once for all heads of
+// the group, as key (all D columns) and as value (the first `rank`).  32-bit arithmetic throughout.
+//   scores   thread (warp w, lane) holds S[2w][key lane] and S[2w+1][key lane]
+//   softmax  per head over the tile by warp shuffles, running maximum and sum per head
+//   output   thread t owns columns (t % 128) + 128 j of heads (t / 128) * 8 .. + 7
+// With more than one split the block leaves (maximum, sum, unnormalised output) per head in `work`
+// [request][split][head][rank + 2] and latent_decode_merge adds the splits in order.
+constexpr int LD_HEADS = 16, LD_KEYS = 32, LD_THREADS = 256, LD_MAXC = 5;   // rank <= 128 * LD_MAXC
+
+template <typename T>
+__global__ void __launch_bounds__(LD_THREADS)
+latent_decode_kernel(T* __restrict__ out, int out_stride, float* __restrict__ work, const T* __restrict__ q, int q_stride,
+                     const T* __restrict__ cache, const int* __restrict__ block_tables, int bt_stride,
+                     const int* __restrict__ cu_q, const int* __restrict__ kv_lens, const int* __restrict__ dec_seq,
+                     int heads, int D, int rank, int page_size, float scale, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  float* qs = sm;                              // [LD_HEADS][D]
+  float* ks = qs + LD_HEADS * D;               // [LD_KEYS][D + 1]
+  float* ps = ks + LD_KEYS * (D + 1);          // [LD_HEADS][LD_KEYS]
+  float* al = ps + LD_HEADS * LD_KEYS;         // [LD_HEADS] rescale of this tile
+  const int split = blockIdx.x, seq = dec_seq[blockIdx.y], h0 = blockIdx.z * LD_HEADS;
+  const int nh = min(LD_HEADS, heads - h0);
+  const int tok = cu_q[seq], kv_len = kv_lens[seq];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int* bt = block_tables + (size_t)seq * bt_stride;
+  // this split's keys: whole tiles, dealt out evenly
+  const int tiles = (kv_len + LD_KEYS - 1) / LD_KEYS;
+  const int per = (tiles + splits - 1) / splits;
+  const int t_begin = split * per, t_end = min(tiles, t_begin + per);
+
+  for (int e = tid; e < LD_HEADS * D; e += LD_THREADS) {
+    const int h = e / D, c = e - h * D;
+    qs[e] = h < nh ? to_f32(q[(size_t)tok * q_stride + (size_t)(h0 + h) * D + c]) : 0.f;
+  }
+  const int ha = 2 * warp, hb = 2 * warp + 1;          // the two heads whose scores this thread forms
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+  const int col = tid & 127, hg = (tid >> 7) * 8;       // output columns col + 128 j of heads hg .. hg + 7
+  float acc[8][LD_MAXC];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < LD_MAXC; ++j) acc[i][j] = 0.f;
+
+  for (int tile = t_begin; tile < t_end; ++tile) {
+    const int k0 = tile * LD_KEYS;
+    __syncthreads();     // the tile before is consumed (the first time: qs is written)
+    for (int e = tid; e < LD_KEYS * D; e += LD_THREADS) {
+      const int kk = e / D, c = e - kk * D, j = k0 + kk;
+      float v = 0.f;
+      if (j < kv_len) {
+        const int page = bt[j / page_size];
+        if (page >= 0) v = to_f32(cache[((size_t)page * page_size + (j % page_size)) * D + c]);
+      }
+      ks[kk * (D + 1) + c] = v;
+    }
+    __syncthreads();
+    float sa = 0.f, sb = 0.f;
+    {
+      const float* kr = ks + lane * (D + 1);
+      const float* qa = qs + ha * D;
+      const float* qb = qs + hb * D;
+      for (int c = 0; c < D; ++c) {
+        const float kv = kr[c];
+        sa = fmaf(qa[c], kv, sa);
+        sb = fmaf(qb[c], kv, sb);
+      }
+    }
+    const bool live = k0 + lane < kv_len;
+    sa = live ? sa * scale : -INFINITY;
+    sb = live ? sb * scale : -INFINITY;
+    const float na = fmaxf(m_a, warp_max(sa)), nb = fmaxf(m_b, warp_max(sb));    // finite: a tile has a live key
+    const float pa = live ? expf(sa - na) : 0.f, pb = live ? expf(sb - nb) : 0.f;
+    const float ra = expf(m_a - na), rb = expf(m_b - nb);                        // exp(-inf) = 0 the first time
+    l_a = l_a * ra + warp_sum(pa);
+    l_b = l_b * rb + warp_sum(pb);
+    m_a = na;
+    m_b = nb;
+    ps[ha * LD_KEYS + lane] = pa;
+    ps[hb * LD_KEYS + lane] = pb;
+    if (lane == 0) {
+      al[ha] = ra;
+      al[hb] = rb;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float r = al[hg + i];
+#pragma unroll
+      for (int j = 0; j < LD_MAXC; ++j) acc[i][j] *= r;
+    }
+    for (int kk = 0; kk < LD_KEYS; ++kk) {
+      float v[LD_MAXC];
+#pragma unroll
+      for (int j = 0; j < LD_MAXC; ++j) v[j] = col + 128 * j < rank ? ks[kk * (D + 1) + col + 128 * j] : 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float p = ps[(hg + i) * LD_KEYS + kk];
+#pragma unroll
+        for (int j = 0; j < LD_MAXC; ++j) acc[i][j] = fmaf(p, v[j], acc[i][j]);
+      }
+    }
+  }
+  // running maximum and sum of every head, for the threads that own its columns
+  __syncthreads();
+  if (lane == 0) {
+    ps[ha] = m_a;
+    ps[hb] = m_b;
+    ps[LD_HEADS + ha] = l_a;
+    ps[LD_HEADS + hb] = l_b;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int h = hg + i;
+    if (h >= nh) continue;
+    const float mh = ps[h], lh = ps[LD_HEADS + h];
+    if (splits == 1) {
+      const float inv = 1.0f / lh;
+      T* o = out + (size_t)tok * out_stride + (size_t)(h0 + h) * rank;
+#pragma unroll
+      for (int j = 0; j < LD_MAXC; ++j)
+        if (col + 128 * j < rank) o[col + 128 * j] = from_f32<T>(acc[i][j] * inv);
+    } else {
+      float* w = work + (((size_t)blockIdx.y * splits + split) * heads + (h0 + h)) * (rank + 2);
+      if (col == 0) {
+        w[0] = mh;      // -inf and 0 when the split had no keys
+        w[1] = lh;
+      }
+#pragma unroll
+      for (int j = 0; j < LD_MAXC; ++j)
+        if (col + 128 * j < rank) w[2 + col + 128 * j] = acc[i][j];
+    }
+  }
+}
+
+// out[token, head, :] = sum over splits of exp(m_s - m) O_s / sum over splits of exp(m_s - m) l_s, splits in order.
+template <typename T>
+__global__ void latent_decode_merge_kernel(T* __restrict__ out, int out_stride, const float* __restrict__ work,
+                                           const int* __restrict__ cu_q, const int* __restrict__ dec_seq, int heads,
+                                           int rank, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int tok = cu_q[dec_seq[r]];
+  const float* w = work + ((size_t)r * splits * heads + h) * (rank + 2);
+  const size_t stride = (size_t)heads * (rank + 2);
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, w[s * stride]);
+  float l = 0.f;
+  for (int s = 0; s < splits; ++s) l += w[s * stride + 1] * expf(w[s * stride] - m);
+  const float inv = 1.0f / l;
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+    float o = 0.f;
+    for (int s = 0; s < splits; ++s) o = fmaf(w[s * stride + 2 + c], expf(w[s * stride] - m), o);
+    out[(size_t)tok * out_stride + (size_t)h * rank + c] = from_f32<T>(o * inv);
+  }
 }
 }  // namespace
+
+extern "C" long long zi_latent_decode_workspace_floats(int n_dec, int heads, int rank, int splits) {
+  return splits > 1 ? (long long)n_dec * splits * heads * (rank + 2) : 0;
+}
+
+extern "C" int zi_latent_decode(void* out, int out_stride, float* work, const void* q, int q_stride, int dtype,
+                                const void* cache, const int* block_tables, int bt_stride, const int* cu_q,
+                                const int* kv_lens, const int* dec_seq, int n_dec, int heads, int D, int rank,
+                                int page_size, float scale, int splits, cudaStream_t stream) {
+  if (n_dec <= 0) return 0;
+  if (rank > 128 * LD_MAXC || rank > D) return zi_refuse("latent_decode: a latent of %d values (rows of %d) is more than this kernel holds", rank, D);
+  if (splits < 1 || (splits > 1 && !work)) return zi_refuse("latent_decode: %d splits need a workspace", splits);
+  const size_t smem = (size_t)(LD_HEADS * D + LD_KEYS * (D + 1) + LD_HEADS * LD_KEYS + LD_HEADS) * sizeof(float);
+  dim3 grid(splits, n_dec, (heads + LD_HEADS - 1) / LD_HEADS);
+  ZI_DISPATCH_DTYPE(dtype, TT, {
+    auto kern = latent_decode_kernel<TT>;
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return zi_refuse("latent_decode: cannot get %zu bytes of shared memory", smem);
+    zi_launch(kern, dim3(grid), dim3(LD_THREADS), smem, stream, (TT*)out, out_stride, work, (const TT*)q, q_stride,
+              (const TT*)cache, block_tables, bt_stride, cu_q, kv_lens, dec_seq, heads, D, rank, page_size, scale, splits);
+    if (splits > 1)
+      zi_launch(latent_decode_merge_kernel<TT>, dim3(n_dec, heads), dim3(128), 0, stream, (TT*)out, out_stride,
+                (const float*)work, cu_q, dec_seq, heads, rank, splits);
+  });
+  return zi_check_launch("latent_decode");
+}
 
 extern "C" int zi_latent_gather(void* keys, void* values_t, const void* cache, int dtype, const int* block_table,
                                 int page_size, int kv_len, int kv_pad, int D, int rank, cudaStream_t stream) {

@@ -96,7 +96,83 @@ __global__ void rglru_scan_kernel(T* __restrict__ out, int ldo, const float* __r
   for (int j = 0; j < taps - 1; ++j) keep[j] = conv_input(x, ldx, xb, st, C, taps, n, tok0, taps - 1 - j, c);
   for (int j = 0; j < taps - 1; ++j) st[(size_t)j * C + c] = keep[j];
 }
+
+// A step in which every request brings one token: convolution, both gates, the recurrence and the gated
+// output in one kernel.  Block (channel block b, request s); a warp takes gate rows in turn, its lanes
+// stride over the block's inputs and the partial sums meet in a fixed order.
+//   wg [blocks][2 bw][bw]: per block the recurrence gate's matrix above the input gate's.
+template <typename T, typename TW>
+__global__ void __launch_bounds__(256)
+rglru_decode_kernel(T* __restrict__ out, int ldo, const T* __restrict__ yx, int ld, const float* __restrict__ yb,
+                    const float* __restrict__ xb, const float* __restrict__ kern, const float* __restrict__ cb,
+                    const TW* __restrict__ wg, int bw, const float* __restrict__ rb, const float* __restrict__ ib,
+                    const float* __restrict__ lam, float decay_scale, float* __restrict__ state, int C, int taps,
+                    const int* __restrict__ state_slots) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sh[];
+  float* u = sh;               // [bw]
+  float* gate = sh + bw;       // [2 bw]
+  const int b = blockIdx.x, s = blockIdx.y, c0 = b * bw;
+  float* st = state + (size_t)state_slots[s] * taps * C;
+  const T* y = yx + (size_t)s * ld;          // this request's row: y branch, then x branch
+  const T* x = y + C;
+  for (int o = threadIdx.x; o < bw; o += blockDim.x) {
+    const int c = c0 + o;
+    const float xin = to_f32(x[c]) + xb[c];
+    float acc = cb[c];
+    for (int j = 0; j < taps - 1; ++j) acc = fmaf(kern[(size_t)c * taps + j], st[(size_t)j * C + c], acc);
+    u[o] = fmaf(kern[(size_t)c * taps + taps - 1], xin, acc);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const TW* w = wg + (size_t)b * 2 * bw * bw;
+  for (int row = warp; row < 2 * bw; row += nwarp) {
+    float acc = 0.f;
+    for (int i = lane; i < bw; i += 32) acc = fmaf(to_f32(w[(size_t)row * bw + i]), u[i], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) gate[row] = acc;
+  }
+  __syncthreads();
+  for (int o = threadIdx.x; o < bw; o += blockDim.x) {
+    const int c = c0 + o;
+    const float r = sigmoid_f32(gate[o] + rb[c]);
+    const float i = sigmoid_f32(gate[bw + o] + ib[c]);
+    const float log_a = -decay_scale * softplus_f32(lam[c]) * r;
+    const float a = expf(log_a);
+    const float mult = sqrtf(-expm1f(2.0f * log_a));
+    const float S = fmaf(a, st[(size_t)(taps - 1) * C + c], mult * (i * u[o]));
+    st[(size_t)(taps - 1) * C + c] = S;
+    out[(size_t)s * ldo + c] = from_f32<T>(S * gelu_tanh_f32(to_f32(y[c]) + yb[c]));
+    // the carried inputs move up by one; the newest is this token's
+    for (int j = 0; j + 1 < taps - 1; ++j) st[(size_t)j * C + c] = st[(size_t)(j + 1) * C + c];
+    if (taps > 1) st[(size_t)(taps - 2) * C + c] = to_f32(x[c]) + xb[c];
+  }
+}
 }  // namespace
+
+extern "C" int zi_rglru_decode(void* out, int ldo, const void* yx, int ld, int dtype, const float* yb, const float* xb,
+                               const float* kern, const float* cb, const void* wg, int wg_dtype, int block_width,
+                               const float* rb, const float* ib, const float* lam, float decay_scale, float* state,
+                               int C, int taps, const int* state_slots, int n_seqs, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (taps < 1 || taps > 9) return zi_refuse("rglru_decode: 1 to 9 taps, got %d", taps);
+  if (block_width <= 0 || C % block_width) return zi_refuse("rglru_decode: %d channels do not divide into blocks of %d", C, block_width);
+  const size_t smem = (size_t)3 * block_width * sizeof(float);
+  if (smem > 48 * 1024) return zi_refuse("rglru_decode: blocks of %d channels are more than this kernel holds", block_width);
+  dim3 grid(C / block_width, n_seqs);
+  using bf = __nv_bfloat16;
+#define ZI_RGLRU_DECODE(TT, TW)                                                                                      \
+  zi_launch(rglru_decode_kernel<TT, TW>, dim3(grid), dim3(256), smem, stream, (TT*)out, ldo, (const TT*)yx, ld, yb, xb, \
+            kern, cb, (const TW*)wg, block_width, rb, ib, lam, decay_scale, state, C, taps, state_slots)
+  if (dtype == ZI_F32 && wg_dtype == ZI_F32) ZI_RGLRU_DECODE(float, float);
+  else if (dtype == ZI_F32 && wg_dtype == ZI_BF16) ZI_RGLRU_DECODE(float, bf);
+  else if (dtype == ZI_BF16 && wg_dtype == ZI_F32) ZI_RGLRU_DECODE(bf, float);
+  else if (dtype == ZI_BF16 && wg_dtype == ZI_BF16) ZI_RGLRU_DECODE(bf, bf);
+  else return zi_refuse("rglru_decode: unknown dtype tags %d, %d", dtype, wg_dtype);
+#undef ZI_RGLRU_DECODE
+  return zi_check_launch("rglru_decode");
+}
 
 extern "C" int zi_causal_conv(float* u, const void* x, int ldx, int dtype, const float* xb, const float* kern,
                               const float* cb, const float* state, int C, int taps, const int* cu_q,

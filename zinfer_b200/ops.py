@@ -382,11 +382,13 @@ def _sm_count(device: torch.device) -> int:
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-           out: Optional[torch.Tensor] = None, allow_partials: bool = False):
+           out: Optional[torch.Tensor] = None, allow_partials: bool = False, fresh_weight: bool = False):
     """``x [M, K] @ weight [N, K]^T`` with 32-bit accumulation.
 
     With ``allow_partials`` a product that was split along K may come back as
-    :class:`Partials` (its consumer adds the splits) instead of a tensor.
+    :class:`Partials` (its consumer adds the splits) instead of a tensor.  ``fresh_weight``:
+    ``weight`` is no weight but the output of an earlier kernel of this step (the tensor-core kernel
+    otherwise requests its first weight tiles before it waits for the kernels before it).
 
     bfloat16 operands that meet TMA's alignment rules go to the tcgen05 kernel; float32
     operands (the true 32-bit path), mixed types and unaligned shapes go to the
@@ -408,7 +410,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
                           2 * M * N * K):
             _check(lib().zi_gemm_tcgen05(_ptr(out), _tag(out) if out is not None else BF16, _ptr(x), _ptr(weight), M, N, K,
                                          x.stride(0), weight.stride(0), out.stride(0) if out is not None else N, _ptr(ws),
-                                         ctypes.c_longlong(need), sms, 1 if defer else 0, _stream()), "linear (tcgen05)")
+                                         ctypes.c_longlong(need), sms, (1 if defer else 0) | (2 if fresh_weight else 0),
+                                         _stream()), "linear (tcgen05)")
         return Partials(ws.view(plan[2], M, N)) if defer else out
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
@@ -648,6 +651,30 @@ def rglru_scan(u: torch.Tensor, gates: torch.Tensor, block_width: int, r_bias: t
     return out
 
 
+def rglru_decode(yx: torch.Tensor, y_bias: torch.Tensor, x_bias: torch.Tensor, kernel: torch.Tensor, bias: torch.Tensor,
+                 w_gates: torch.Tensor, r_bias: torch.Tensor, i_bias: torch.Tensor, lam: torch.Tensor,
+                 decay_scale: float, state: torch.Tensor, step) -> torch.Tensor:
+    """:func:`causal_conv`, the gates' products and :func:`rglru_scan` in one kernel, for a step in which every
+    request brings one token.  ``yx`` [n, 2C]: the y branch, then the x branch, before their biases;
+    ``w_gates`` [blocks, 2 * block_width, block_width]."""
+    n, two_c = yx.shape
+    C = two_c // 2
+    taps = state.shape[1]
+    B, two_bw, bw = w_gates.shape
+    _need(yx.is_contiguous() and B * bw == C and two_bw == 2 * bw and w_gates.is_contiguous()
+          and state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (taps, C),
+          "rglru_decode: shapes")
+    _need(n == step.n_seqs, "rglru_decode: every request brings exactly one token")
+    out = torch.empty((n, C), dtype=yx.dtype, device=yx.device)
+    with _prof.region("rglru decode (conv, gates, recurrence)", lambda: _nb(w_gates, yx, out) + 2 * n * taps * C * 4,
+                      4 * n * C * bw):
+        _check(lib().zi_rglru_decode(_ptr(out), out.stride(0), _ptr(yx), yx.stride(0), _tag(yx), _ptr(y_bias), _ptr(x_bias),
+                                     _ptr(kernel), _ptr(bias), _ptr(w_gates), _tag(w_gates), bw, _ptr(r_bias), _ptr(i_bias),
+                                     _ptr(lam), ctypes.c_float(decay_scale), _ptr(state), C, taps, _ptr(step.state_slots),
+                                     n, _stream()), "rglru_decode")
+    return out
+
+
 # ----------------------------------------------------------------- latent attention
 def latent_prepare(proj: torch.Tensor, heads: int, dim: int, rot_dim: int, rank: int, rot_dims: int,
                    c_weight: torch.Tensor, eps: float, cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor,
@@ -686,14 +713,34 @@ def latent_attention(q_eff: torch.Tensor, cache: torch.Tensor, block_tables: tor
     In float32, and for requests that bring few tokens, the exact kernel on the CUDA cores.  In bfloat16 a
     request's longer portion runs as two tcgen05 products: its cached rows are gathered from the pages (once
     as they are, once with the latent part transposed), S = Q rows^T in 32-bit, a causal softmax in 32-bit
-    that writes P in bfloat16, then P times the latent part.  The scores of a portion against all its keys
+    that writes each weight as a high and a low bfloat16 part (16 bits together: rounding the weights to 8
+    bits moved results by more than the rest of a bfloat16 layer does), then [high | low] times the latent
+    part held twice.  The scores of a portion against all its keys
     pass through memory; a portion of 2,048 tokens of 16 heads against 2,048 keys holds 268 MB for that."""
     T = q_eff.shape[0]
     D = cache.shape[-1]
     _need(q_eff.shape[1] == heads * D and q_eff.is_contiguous() and cache.is_contiguous() and cache.dtype == q_eff.dtype,
           "latent_attention: shapes")
     out = torch.empty((T, heads * rank), dtype=q_eff.dtype, device=q_eff.device)
-    skip_from = 0
+    skip_from = skip_single = 0
+    n_dec = int(getattr(step, "n_dec", 0) or 0)
+    if n_dec > 0 and not window and rank <= 640 and ATTENTION_BACKEND != "generic":
+        # requests that bring one token: split-key kernel, every cached row fetched once for 16 heads
+        splits = latent_decode_splits(n_dec, -(-heads // 16), _sm_count(q_eff.device), step.max_kv_len,
+                                      fixed=q_eff.dtype == torch.float32)
+        need = lib().zi_latent_decode_workspace_floats(n_dec, heads, rank, splits)
+        ws = torch.empty((need,), dtype=torch.float32, device=q_eff.device) if need else None
+        with _prof.region("latent attention (decode, split keys)",
+                          lambda: sum((c + 1) * D for q_, c in zip(step.q_lens, step.ctx_lens) if q_ == 1) * q_eff.element_size(),
+                          sum(2 * heads * (c + 1) * (D + rank) for q_, c in zip(step.q_lens, step.ctx_lens) if q_ == 1)):
+            _check(lib().zi_latent_decode(
+                _ptr(out), out.stride(0), _ptr(ws), _ptr(q_eff), q_eff.stride(0), _tag(q_eff), _ptr(cache),
+                _ptr(_i32(block_tables, "block_tables")), block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens),
+                _ptr(step.dec_seq), n_dec, heads, D, rank, page_size, ctypes.c_float(scale), splits, _stream()),
+                "latent_decode")
+        if n_dec == step.n_seqs:
+            return out
+        skip_single = 1
     if (q_eff.dtype == torch.bfloat16 and not window and GEMM_BACKEND != "simt" and ATTENTION_BACKEND != "generic"
             and D % 8 == 0 and rank % 8 == 0 and getattr(step, "q_lens", None)
             and max(step.q_lens) >= LATENT_TENSOR_MIN_TOKENS):
@@ -704,15 +751,27 @@ def latent_attention(q_eff: torch.Tensor, cache: torch.Tensor, block_tables: tor
                 _latent_attention_portion(q_eff[t0:t0 + n], out[t0:t0 + n], cache, block_tables[s], heads, rank, D,
                                           page_size, ctx, scale)
             t0 += n
-        if all(n >= skip_from for n in step.q_lens):
+        if all(n >= skip_from or (n == 1 and skip_single) for n in step.q_lens):
             return out
     with _prof.region("latent attention (exact, CUDA cores)"):
         _check(lib().zi_paged_attention_v(
             _ptr(out), out.stride(0), _ptr(q_eff), q_eff.stride(0), _tag(q_eff), _ptr(cache), _ptr(cache),
             _ptr(_i32(block_tables, "block_tables")), block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens),
             _ptr(step.tile_seq), _ptr(step.tile_q0), step.tile_seq.shape[0], heads, 1, D, rank, D, page_size,
-            int(window or 0), ctypes.c_float(scale), skip_from, _stream()), "latent_attention")
+            int(window or 0), ctypes.c_float(scale), skip_from, skip_single, _stream()), "latent_attention")
     return out
+
+
+def latent_decode_splits(n_dec: int, head_groups: int, sm_count: int, max_kv_len: Optional[int], fixed: bool = False) -> int:
+    """Key splits of the latent decode kernel: its blocks are (split, request, group of 16 heads), two fit on an
+    SM, and a block walks its keys in tiles of 32; as many splits as fill the GPU about once, at most one per
+    two tiles of the longest request and at most 32.  ``fixed`` (the 32-bit path): always 8, so that the order
+    in which a request's keys are added does not depend on what else is in the batch."""
+    if fixed:
+        return 8
+    tiles = -(-(max_kv_len or 2048) // 32)
+    want = (2 * sm_count) // max(1, n_dec * head_groups)
+    return max(1, min(want, tiles // 2, 32))
 
 
 def _latent_attention_portion(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
@@ -724,16 +783,16 @@ def _latent_attention_portion(q: torch.Tensor, out: torch.Tensor, cache: torch.T
     rows = n * heads
     dev = q.device
     keys = torch.empty((kv_pad, D), dtype=q.dtype, device=dev)
-    values_t = torch.empty((rank, kv_pad), dtype=q.dtype, device=dev)
+    values_t = torch.empty((rank, 2 * kv_pad), dtype=q.dtype, device=dev)    # twice: for the weights' high and low parts
     with _prof.region("latent attention: gather rows", lambda: 2 * _nb(keys) + _nb(values_t)):
         _check(lib().zi_latent_gather(_ptr(keys), _ptr(values_t), _ptr(cache), _tag(cache), _ptr(_i32(block_table, "block_table")),
                                       page_size, kv, kv_pad, D, rank, _stream()), "latent_gather")
-    scores = linear(q.view(rows, D), keys, out_dtype=torch.float32)
-    probs = torch.empty((rows, kv_pad), dtype=q.dtype, device=dev)
+    scores = linear(q.view(rows, D), keys, out_dtype=torch.float32, fresh_weight=True)
+    probs = torch.empty((rows, 2 * kv_pad), dtype=q.dtype, device=dev)
     with _prof.region("latent attention: causal softmax", lambda: _nb(scores, probs)):
         _check(lib().zi_causal_softmax(_ptr(probs), _ptr(scores), _tag(probs), ctypes.c_longlong(rows), heads, ctx, kv_pad,
                                        ctypes.c_float(scale), _stream()), "causal_softmax")
-    linear(probs, values_t, out=out.view(rows, rank))
+    linear(probs, values_t, out=out.view(rows, rank), fresh_weight=True)
 
 
 # ----------------------------------------------------------------------- attention

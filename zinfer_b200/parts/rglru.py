@@ -73,6 +73,11 @@ class RGLRUMixer(Mixer):
     def forward(self, x, step, cache):
         T, W, B, bw = x.shape[0], self.width, self.blocks, self.bw
         yx = ops.linear(x, self.w_yx, out_dtype=self.ctx.dtype)         # [T, 2W]: y branch, then x branch
+        if step.all_decode and step.n_seqs == T:
+            # one token per request: convolution, gates and recurrence are one kernel
+            mixed = ops.rglru_decode(yx, self.y_bias, self.x_bias, self.conv, self.conv_bias, self.w_gates, self.r_bias,
+                                     self.i_bias, self.lam, self.decay_scale, cache.state, step)
+            return ops.linear(mixed, self.w_o, out_dtype=self.ctx.dtype, allow_partials=True)
         y, xb = yx[:, :W], yx[:, W:]
         u = ops.causal_conv(xb, self.x_bias, self.conv, self.conv_bias, cache.state, step)     # float32 [T, W]
         gates = torch.empty((T, B, 2 * bw), dtype=torch.float32, device=x.device)
