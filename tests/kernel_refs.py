@@ -183,6 +183,14 @@ def moe_route(logits, correction, top, renormalize=False):
     return chosen.to(torch.int32), weight
 
 
+def moe_router(x, w_router, correction, top, renormalize=False):
+    return moe_route(linear(x, w_router, out_dtype=torch.float32), correction, top, renormalize)
+
+
+def linear_few_rows_ok(x, weight):
+    return False
+
+
 def moe_align(chosen, experts, tile_rows):
     T, top = chosen.shape
     flat = chosen.reshape(-1).tolist()

@@ -310,6 +310,21 @@ def test_kernels_of_the_new_parts_against_plain_formulas():
         else:
             assert rt[pr[p]] == p // 3 and te[pr[p] // 16] == e
     assert len({r for r in pr if r >= 0}) == sum(e < 9 for e in flat)
+    # the router's product and the choice in one kernel against the product followed by the choice
+    xr, wr = torch.randn(37, 52, generator=gen).to(torch.bfloat16).to(DEV), torch.randn(11, 52, generator=gen).to(torch.bfloat16).to(DEV)
+    c2, w2 = ops.moe_router(xr, wr, corr.to(DEV), 3)
+    c1, w1 = ops.moe_route(ops.linear_cuda_cores(xr, wr, out_dtype=torch.float32), corr.to(DEV), 3)
+    assert torch.equal(c1, c2) and torch.allclose(w1, w2, rtol=1e-5, atol=1e-7)
+    # few rows per expert: the memory-bound grouped product against the general one, on the same layout
+    for dt in (torch.float32, torch.bfloat16):
+        xe = torch.randn(37, 40, generator=gen).to(dt).to(DEV)
+        we = torch.randn(9, 28, 40, generator=gen).to(dt).to(DEV)
+        a = torch.zeros((row_token.numel(), 28), dtype=torch.float32, device=DEV)
+        b = torch.zeros_like(a)
+        ops.linear_grouped(xe, we, a, row_token, tile_expert, n_tiles, 16, relu2=True)
+        assert ops.linear_few_rows_ok(xe, we)
+        ops.linear_few_rows(xe, we, b, row_token, tile_expert, n_tiles, relu2=True)
+        torch.testing.assert_close(b, a, rtol=1e-5, atol=1e-5)
     # recurrence: two requests of 9 and 4 tokens continue from given states; 5 channels in one block, 3 taps
     T, C, taps = 13, 5, 3
     step = SimpleNamespace(cu_q=torch.tensor([0, 9, 13], dtype=torch.int32, device=DEV),
@@ -354,6 +369,35 @@ def test_kernels_of_the_new_parts_against_plain_formulas():
     got = ops.rglru_decode(yx, yb, xb, kern, cb, wg, rb, ib, lam, 8.0, sb, step1)
     torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(sb, sa, rtol=1e-5, atol=1e-6)
+
+
+@gpu
+def test_recurrence_in_chunks_against_the_walk():
+    """Three requests of 70, 1 and 89 tokens in one bfloat16 step (the recurrence runs in chunks of the flat
+    batch, across the requests' borders) against the same step in float32 (token by token)."""
+    from types import SimpleNamespace
+
+    from zinfer_b200 import ops
+
+    gen = torch.Generator().manual_seed(9)
+    T, B, bw, taps = 160, 2, 20, 4
+    C = B * bw
+    step = SimpleNamespace(cu_q=torch.tensor([0, 70, 71, 160], dtype=torch.int32, device=DEV), n_seqs=3,
+                           state_slots=torch.tensor([2, 0, 3], dtype=torch.int32, device=DEV))
+    dev = lambda t: t.to(DEV).contiguous()
+    yx = torch.randn(T, 2 * C, generator=gen).to(torch.bfloat16)
+    yb, xb, rb, ib = (dev(0.3 * torch.randn(C, generator=gen)) for _ in range(4))
+    lam = dev(torch.randn(C, generator=gen) - 3.0)                      # slow decay: chunks feed one another
+    u, gates = dev(torch.randn(T, C, generator=gen)), dev(torch.randn(T, B, 2 * bw, generator=gen))
+    state0 = torch.randn(4, taps, C, generator=gen)
+    outs, states = [], []
+    for dtype in (torch.float32, torch.bfloat16):
+        st, v = dev(state0), dev(yx.to(dtype))
+        outs.append(ops.rglru_scan(u, gates, bw, rb, ib, lam, 8.0, v[:, :C], yb, v[:, C:], xb, st, step).float())
+        states.append(st)
+    torch.testing.assert_close(outs[1], outs[0], rtol=1e-2, atol=1e-2)          # the result's own rounding to bfloat16
+    torch.testing.assert_close(states[1], states[0], rtol=1e-5, atol=1e-6)      # the carried state is 32-bit in both
+    assert torch.equal(states[1][1].cpu(), state0[1])
 
 
 @gpu

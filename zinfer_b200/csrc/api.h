@@ -67,6 +67,13 @@ int zi_rglru_scan(void* out, int ldo, const float* u, const float* gates, int bl
                   const void* x, int ldx, const float* xb, int dtype, float* state, int C, int taps, const int* cu_q,
                   const int* state_slots, int n_seqs, cudaStream_t stream);
 
+// The same recurrence in chunks of `chunk` tokens of the flat batch (four small kernels; sums associated per chunk).
+long long zi_rglru_chunked_workspace_floats(int T, int C, int n_seqs, int chunk);
+int zi_rglru_scan_chunked(void* out, int ldo, float* work, const float* u, const float* gates, int block_width,
+                          const float* rb, const float* ib, const float* lam, float decay_scale, const void* y, int ldy,
+                          const float* yb, const void* x, int ldx, const float* xb, int dtype, float* state, int C,
+                          int taps, const int* cu_q, const int* state_slots, int n_seqs, int T, int chunk,
+                          cudaStream_t stream);
 // One token per request: convolution, gates, recurrence and gated output in one kernel.  yx rows: y branch, x branch.
 int zi_rglru_decode(void* out, int ldo, const void* yx, int ld, int dtype, const float* yb, const float* xb,
                     const float* kern, const float* cb, const void* wg, int wg_dtype, int block_width, const float* rb,
@@ -118,6 +125,11 @@ int zi_latent_decode(void* out, int out_stride, float* work, const void* q, int 
 // Mixture of experts: choice and weights per token, the pairs laid out by expert, the weighted sum.
 int zi_moe_route(int* chosen, float* weight, const float* logits, const float* correction, int T, int NR, int top,
                  int renormalize, cudaStream_t stream);
+int zi_moe_router(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w, int w_dtype,
+                  const float* correction, int T, int K, int NR, int top, int renormalize, cudaStream_t stream);
+int zi_moe_few_rows(void* out, int out_dtype, int ldo, const void* x, int dtype, int ldx, const void* w,
+                    const int* row_src, const int* tile_group, const int* n_tiles_dev, int max_tiles, int N, int K,
+                    int relu2, cudaStream_t stream);
 int zi_moe_align(const int* chosen, int P, int top, int E, int tile_rows, int cap_tiles, int* row_token, int* row_self,
                  int* pair_row, int* tile_expert, int* n_tiles, cudaStream_t stream);
 int zi_gather_rows(void* out, const void* x, int dtype, const int* row_src, int rows, int width, int ldx,

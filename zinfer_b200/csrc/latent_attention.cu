@@ -172,14 +172,15 @@ latent_decode_kernel(T* __restrict__ out, int out_stride, float* __restrict__ wo
   const int tok = cu_q[seq], kv_len = kv_lens[seq];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int* bt = block_tables + (size_t)seq * bt_stride;
+  const bool vec8 = sizeof(T) == 2 && D % 8 == 0 && ((uintptr_t)cache & 15) == 0;
   // this split's keys: whole tiles, dealt out evenly
   const int tiles = (kv_len + LD_KEYS - 1) / LD_KEYS;
   const int per = (tiles + splits - 1) / splits;
   const int t_begin = split * per, t_end = min(tiles, t_begin + per);
 
-  for (int e = tid; e < LD_HEADS * D; e += LD_THREADS) {
-    const int h = e / D, c = e - h * D;
-    qs[e] = h < nh ? to_f32(q[(size_t)tok * q_stride + (size_t)(h0 + h) * D + c]) : 0.f;
+  for (int h = warp; h < LD_HEADS; h += LD_THREADS / 32) {       // a warp per query row
+    const T* qr = q + (size_t)tok * q_stride + (size_t)(h0 + h) * D;
+    for (int c = lane; c < D; c += 32) qs[h * D + c] = h < nh ? to_f32(qr[c]) : 0.f;
   }
   const int ha = 2 * warp, hb = 2 * warp + 1;          // the two heads whose scores this thread forms
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
@@ -193,14 +194,28 @@ latent_decode_kernel(T* __restrict__ out, int out_stride, float* __restrict__ wo
   for (int tile = t_begin; tile < t_end; ++tile) {
     const int k0 = tile * LD_KEYS;
     __syncthreads();     // the tile before is consumed (the first time: qs is written)
-    for (int e = tid; e < LD_KEYS * D; e += LD_THREADS) {
-      const int kk = e / D, c = e - kk * D, j = k0 + kk;
-      float v = 0.f;
-      if (j < kv_len) {
-        const int page = bt[j / page_size];
-        if (page >= 0) v = to_f32(cache[((size_t)page * page_size + (j % page_size)) * D + c]);
+    for (int kk = warp; kk < LD_KEYS; kk += LD_THREADS / 32) {      // a warp per cached row: one page lookup
+      const int j = k0 + kk;
+      const int page = j < kv_len ? bt[j / page_size] : -1;
+      float* dst = ks + kk * (D + 1);
+      if (page < 0) {
+        for (int c = lane; c < D; c += 32) dst[c] = 0.f;
+      } else {
+        const T* row = cache + ((size_t)page * page_size + (j % page_size)) * D;
+        if (vec8) {        // 16 bytes a lane
+          for (int c = lane * 8; c < D; c += 256) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(row + c);
+            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              dst[c + 2 * i] = __low2float(p2[i]);
+              dst[c + 2 * i + 1] = __high2float(p2[i]);
+            }
+          }
+        } else {
+          for (int c = lane; c < D; c += 32) dst[c] = to_f32(row[c]);
+        }
       }
-      ks[kk * (D + 1) + c] = v;
     }
     __syncthreads();
     float sa = 0.f, sb = 0.f;

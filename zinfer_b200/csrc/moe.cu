@@ -13,19 +13,11 @@ namespace {
 constexpr int ROUTE_WARPS = 4;
 
 // One warp per token.  Sums run over a fixed order of lanes, so a token's choice does not depend on
-// the batch.  Ties go to the lower index.
-__global__ void __launch_bounds__(ROUTE_WARPS * 32)
-moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, const float* __restrict__ logits,
-                 const float* __restrict__ correction, int T, int NR, int top, int renormalize) {
-  pdl_launch_dependents();
-  pdl_wait();
-  extern __shared__ float sm[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * ROUTE_WARPS + warp;
-  if (t >= T) return;
-  float* score = sm + (size_t)warp * 2 * NR;   // softmax scores
-  float* pick = score + NR;                    // scores plus correction; -inf once chosen
-  const float* z = logits + (size_t)t * NR;
+// the batch.  Ties go to the lower index.  z: the token's NR logits; score, pick: NR floats each of
+// shared memory for this warp.
+__device__ __forceinline__ void route_token(int* __restrict__ chosen, float* __restrict__ weight, const float* z,
+                                            float* score, float* pick, const float* __restrict__ correction, int t,
+                                            int NR, int top, int renormalize, int lane) {
   float m = -INFINITY;
   for (int j = lane; j < NR; j += 32) m = fmaxf(m, z[j]);
   m = warp_max(m);
@@ -76,6 +68,110 @@ moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, const flo
   if (renormalize && lane == 0) {
     const float r = 1.0f / total;
     for (int k = 0; k < top; ++k) weight[(size_t)t * top + k] *= r;
+  }
+}
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, const float* __restrict__ logits,
+                 const float* __restrict__ correction, int T, int NR, int top, int renormalize) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= T) return;
+  float* score = sm + (size_t)warp * 2 * NR;   // softmax scores
+  route_token(chosen, weight, logits + (size_t)t * NR, score, score + NR, correction, t, NR, top, renormalize, lane);
+}
+
+// The router's product and the choice in one kernel, one block per token: the token's row in shared
+// memory as 32-bit values, a warp per router output (lanes stride over the row, partial sums meet in a
+// fixed order), then the first warp chooses.  32-bit multiply-adds whatever the operands' types.
+template <typename TX, typename TW>
+__global__ void __launch_bounds__(128)
+moe_router_kernel(int* __restrict__ chosen, float* __restrict__ weight, const TX* __restrict__ x, int ldx,
+                  const TW* __restrict__ w, const float* __restrict__ correction, int K, int NR, int top,
+                  int renormalize) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  float* xs = sm;              // [K]
+  float* z = sm + K;           // [NR] logits, then [NR] scores, [NR] picks
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f32(x[(size_t)t * ldx + k]);
+  __syncthreads();
+  for (int j = warp; j < NR; j += 4) {
+    const TW* wr = w + (size_t)j * K;
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc = fmaf(xs[k], to_f32(wr[k]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z[j] = acc;
+  }
+  __syncthreads();
+  if (warp == 0) route_token(chosen, weight, z, z + NR, z + 2 * NR, correction, t, NR, top, renormalize, lane);
+}
+
+// Few rows per expert (a decode step): out[r, n] = act(sum_k x[row_src[r], k] * w[e][n][k]) for the rows r of
+// tile `blockIdx.y` (16 rows, one expert e).  A block takes 8 output columns, a warp one: its lanes stream
+// the weight row once in 8-byte pieces and multiply it with all 16 rows, which lie in shared memory as
+// 32-bit values, K_CHUNK columns at a time.  The weights are read once per tile: bound by memory, not by
+// multiply-adds.  Needs K % 4 == 0.  Every output is one sum in a fixed order (lane-strided, then the
+// lanes' partial sums), independent of the batch.
+constexpr int FR_ROWS = 16, FR_COLS = 8, FR_CHUNK = 1024;
+
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+
+template <typename TX, typename TW, typename TO>
+__global__ void __launch_bounds__(FR_COLS * 32)
+moe_few_rows_kernel(TO* __restrict__ out, int ldo, const TX* __restrict__ x, int ldx, const TW* __restrict__ w,
+                    const int* __restrict__ row_src, const int* __restrict__ tile_group,
+                    const int* __restrict__ n_tiles_dev, int N, int K, int relu2) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if ((int)blockIdx.y >= *n_tiles_dev) return;
+  extern __shared__ float xs[];            // [FR_ROWS][FR_CHUNK]
+  __shared__ int src[FR_ROWS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r0 = blockIdx.y * FR_ROWS, n = blockIdx.x * FR_COLS + warp;
+  if (threadIdx.x < FR_ROWS) src[threadIdx.x] = row_src[r0 + threadIdx.x];
+  const TW* wr = w + ((size_t)tile_group[blockIdx.y] * N + (n < N ? n : 0)) * K;
+  float acc[FR_ROWS];
+#pragma unroll
+  for (int r = 0; r < FR_ROWS; ++r) acc[r] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += FR_CHUNK) {
+    const int kc = min(FR_CHUNK, K - k0);
+    __syncthreads();     // the chunk before is consumed; src is written
+    for (int e = threadIdx.x * 4; e < FR_ROWS * kc; e += blockDim.x * 4) {
+      const int r = e / kc, k = e - r * kc;
+      const float4 v = src[r] >= 0 ? load4(x + (size_t)src[r] * ldx + k0 + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(xs + r * FR_CHUNK + k) = v;
+    }
+    __syncthreads();
+    for (int k = lane * 4; k < kc; k += 128) {
+      const float4 wv = load4(wr + k0 + k);
+#pragma unroll
+      for (int r = 0; r < FR_ROWS; ++r) {
+        const float4 xv = *reinterpret_cast<const float4*>(xs + r * FR_CHUNK + k);
+        acc[r] = fmaf(wv.x, xv.x, fmaf(wv.y, xv.y, fmaf(wv.z, xv.z, fmaf(wv.w, xv.w, acc[r]))));
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < FR_ROWS; ++r) {
+    float v = warp_sum(acc[r]);
+    if (lane == 0 && n < N && src[r] >= 0) {
+      if (relu2) {
+        v = fmaxf(v, 0.f);
+        v *= v;
+      }
+      out[(size_t)(r0 + r) * ldo + n] = from_f32<TO>(v);
+    }
   }
 }
 
@@ -176,6 +272,58 @@ extern "C" int zi_moe_route(int* chosen, float* weight, const float* logits, con
   zi_launch(moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream, chosen,
             weight, logits, correction, T, NR, top, renormalize);
   return zi_check_launch("moe_route");
+}
+
+extern "C" int zi_moe_router(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w, int w_dtype,
+                             const float* correction, int T, int K, int NR, int top, int renormalize,
+                             cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (top <= 0 || top > NR) return zi_refuse("moe_router: %d of %d outputs cannot be chosen", top, NR);
+  const size_t smem = (size_t)(K + 3 * NR) * sizeof(float);
+  if (smem > 200 * 1024) return zi_refuse("moe_router: rows of %d values and %d outputs are more than this kernel holds", K, NR);
+  using bf = __nv_bfloat16;
+#define ZI_ROUTER(TX, TW)                                                                                          \
+  do {                                                                                                             \
+    auto kern = moe_router_kernel<TX, TW>;                                                                         \
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+      return zi_refuse("moe_router: cannot get %zu bytes of shared memory", smem);                                 \
+    zi_launch(kern, dim3(T), dim3(128), smem, stream, chosen, weight, (const TX*)x, ldx, (const TW*)w, correction, K, NR, \
+              top, renormalize);                                                                                   \
+  } while (0)
+  if (x_dtype == ZI_F32 && w_dtype == ZI_F32) ZI_ROUTER(float, float);
+  else if (x_dtype == ZI_F32 && w_dtype == ZI_BF16) ZI_ROUTER(float, bf);
+  else if (x_dtype == ZI_BF16 && w_dtype == ZI_F32) ZI_ROUTER(bf, float);
+  else if (x_dtype == ZI_BF16 && w_dtype == ZI_BF16) ZI_ROUTER(bf, bf);
+  else return zi_refuse("moe_router: unknown dtype tags %d, %d", x_dtype, w_dtype);
+#undef ZI_ROUTER
+  return zi_check_launch("moe_router");
+}
+
+// Grouped product for tiles of 16 rows (see moe_few_rows_kernel).  x and w of one type (float32 or bfloat16),
+// out float32 or that type.
+extern "C" int zi_moe_few_rows(void* out, int out_dtype, int ldo, const void* x, int dtype, int ldx, const void* w,
+                               const int* row_src, const int* tile_group, const int* n_tiles_dev, int max_tiles, int N,
+                               int K, int relu2, cudaStream_t stream) {
+  if (max_tiles <= 0 || N <= 0) return 0;
+  if (K % 4 || ldx % 4 || (uintptr_t)x % 16 || (uintptr_t)w % 16)
+    return zi_refuse("moe_few_rows: rows of %d values (pitch %d) are not whole 16-byte pieces", K, ldx);
+  const size_t smem = (size_t)FR_ROWS * FR_CHUNK * sizeof(float);
+  dim3 grid((N + FR_COLS - 1) / FR_COLS, max_tiles);
+  using bf = __nv_bfloat16;
+#define ZI_FEW(TX, TO)                                                                                             \
+  do {                                                                                                             \
+    auto kern = moe_few_rows_kernel<TX, TX, TO>;                                                                   \
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)         \
+      return zi_refuse("moe_few_rows: cannot get %zu bytes of shared memory", smem);                               \
+    zi_launch(kern, dim3(grid), dim3(FR_COLS * 32), smem, stream, (TO*)out, ldo, (const TX*)x, ldx, (const TX*)w, row_src, \
+              tile_group, n_tiles_dev, N, K, relu2);                                                               \
+  } while (0)
+  if (dtype == ZI_F32 && out_dtype == ZI_F32) ZI_FEW(float, float);
+  else if (dtype == ZI_BF16 && out_dtype == ZI_F32) ZI_FEW(bf, float);
+  else if (dtype == ZI_BF16 && out_dtype == ZI_BF16) ZI_FEW(bf, bf);
+  else return zi_refuse("moe_few_rows: operand type %d with results of type %d", dtype, out_dtype);
+#undef ZI_FEW
+  return zi_check_launch("moe_few_rows");
 }
 
 extern "C" int zi_moe_align(const int* chosen, int P, int top, int E, int tile_rows, int cap_tiles, int* row_token,

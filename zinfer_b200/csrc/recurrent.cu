@@ -97,6 +97,119 @@ __global__ void rglru_scan_kernel(T* __restrict__ out, int ldo, const float* __r
   for (int j = 0; j < taps - 1; ++j) st[(size_t)j * C + c] = keep[j];
 }
 
+// ------------------------------------------------------------- the recurrence in chunks (prompts)
+// One thread per channel walking a prompt's tokens one after the other leaves most of the GPU idle.  The
+// recurrence S_t = a_t S_(t-1) + b_t is linear, so the flat batch is cut into chunks of `chunk` tokens:
+//   1. every chunk alone: A = product of its a_t, B = its final state from zero   (blocks: channels x chunks)
+//   2. the chunks' incoming states, one after the other: S_in[k+1] = A[k] S_in[k] + B[k]   (blocks: channels)
+//   3. every chunk again from its S_in, writing the outputs                         (blocks: channels x chunks)
+//   4. per request: the new state and the convolution's carried inputs              (blocks: channels x requests)
+// A request's first token of the step takes the request's carried state as S_(t-1): in the flat recurrence
+// that is a_t = 0 with b_t = a_t * carried + b_t, so chunks may span requests.  The sums are associated
+// differently than in the token-by-token walk (rounding only); the 32-bit path keeps the walk.
+struct GateTerms {
+  float a, b;
+};
+
+__device__ __forceinline__ GateTerms gate_terms(const float* __restrict__ gates, const float* __restrict__ u, size_t row,
+                                                int C, size_t gcol, int bw, float rbias, float ibias, float rate, int c) {
+  const float r = sigmoid_f32(gates[row * 2 * C + gcol] + rbias);
+  const float i = sigmoid_f32(gates[row * 2 * C + gcol + bw] + ibias);
+  const float log_a = rate * r;
+  GateTerms t;
+  t.a = expf(log_a);
+  t.b = sqrtf(-expm1f(2.0f * log_a)) * (i * u[row * C + c]);
+  return t;
+}
+
+// request whose rows hold flat token t
+__device__ __forceinline__ int seq_of_token(const int* __restrict__ cu_q, int n_seqs, int t) {
+  int s = 0, hi = n_seqs - 1;
+  while (s < hi) {
+    const int mid = (s + hi + 1) >> 1;
+    if (cu_q[mid] <= t) s = mid; else hi = mid - 1;
+  }
+  return s;
+}
+
+// passes 1 (WRITE false: A and B of the chunk into ab[chunk][2][C]) and 3 (WRITE true: outputs from s_in[chunk][C],
+// and each request's last state into last[request][C])
+template <typename T, bool WRITE>
+__global__ void rglru_chunk_kernel(T* __restrict__ out, int ldo, float* __restrict__ ab, const float* __restrict__ s_in,
+                                   float* __restrict__ last, const float* __restrict__ u,
+                                   const float* __restrict__ gates, int bw, const float* __restrict__ rb,
+                                   const float* __restrict__ ib, const float* __restrict__ lam, float decay_scale,
+                                   const T* __restrict__ y, int ldy, const float* __restrict__ yb,
+                                   const float* __restrict__ state, int C, int taps, const int* __restrict__ cu_q,
+                                   const int* __restrict__ state_slots, int n_seqs, int T_total, int chunk) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int k = blockIdx.y, t0 = k * chunk, t1 = min(T_total, t0 + chunk);
+  const int b = c / bw, o = c - b * bw;
+  const size_t gcol = (size_t)b * 2 * bw + o;
+  const float rate = -decay_scale * softplus_f32(lam[c]);
+  const float rbias = rb[c], ibias = ib[c], ybias = WRITE ? yb[c] : 0.f;
+  int s = seq_of_token(cu_q, n_seqs, t0);
+  int next_start = cu_q[s + 1];
+  float A = 1.f, S = WRITE ? s_in[(size_t)k * C + c] : 0.f;
+  for (int t = t0; t < t1; ++t) {
+    while (t >= next_start) {        // requests that bring no token have no rows
+      ++s;
+      next_start = cu_q[s + 1];
+    }
+    if (t == cu_q[s]) {              // the request's first token of this step: from its carried state
+      S = state[((size_t)state_slots[s] * taps + (taps - 1)) * C + c];
+      A = 0.f;
+    }
+    const GateTerms g = gate_terms(gates, u, (size_t)t, C, gcol, bw, rbias, ibias, rate, c);
+    S = fmaf(g.a, S, g.b);
+    A *= g.a;
+    if (WRITE) {
+      out[(size_t)t * ldo + c] = from_f32<T>(S * gelu_tanh_f32(to_f32(y[(size_t)t * ldy + c]) + ybias));
+      if (t == next_start - 1) last[(size_t)s * C + c] = S;
+    }
+  }
+  if (!WRITE) {
+    ab[((size_t)k * 2) * C + c] = A;
+    ab[((size_t)k * 2 + 1) * C + c] = S;
+  }
+}
+
+// pass 2: s_in[k] for every chunk.  A chunk that begins with a request's first token has A = 0 there, so
+// what flows in does not matter; chunk 0 always does.
+__global__ void rglru_carry_kernel(float* __restrict__ s_in, const float* __restrict__ ab, int C, int n_chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float S = 0.f;
+  for (int k = 0; k < n_chunks; ++k) {
+    s_in[(size_t)k * C + c] = S;
+    S = fmaf(ab[((size_t)k * 2) * C + c], S, ab[((size_t)k * 2 + 1) * C + c]);
+  }
+}
+
+// pass 4: the requests' new states and carried inputs
+template <typename T>
+__global__ void rglru_finish_kernel(float* __restrict__ state, const float* __restrict__ last, const T* __restrict__ x,
+                                    int ldx, const float* __restrict__ xb, int C, int taps, const int* __restrict__ cu_q,
+                                    const int* __restrict__ state_slots) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int s = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int tok0 = cu_q[s], n = cu_q[s + 1] - tok0;
+  if (n <= 0) return;
+  float* st = state + (size_t)state_slots[s] * taps * C;
+  st[(size_t)(taps - 1) * C + c] = last[(size_t)s * C + c];
+  float keep[8];
+  for (int j = 0; j < taps - 1; ++j) keep[j] = conv_input(x, ldx, xb, st, C, taps, n, tok0, taps - 1 - j, c);
+  for (int j = 0; j < taps - 1; ++j) st[(size_t)j * C + c] = keep[j];
+}
+
 // A step in which every request brings one token: convolution, both gates, the recurrence and the gated
 // output in one kernel.  Block (channel block b, request s); a warp takes gate rows in turn, its lanes
 // stride over the block's inputs and the partial sums meet in a fixed order.
@@ -172,6 +285,39 @@ extern "C" int zi_rglru_decode(void* out, int ldo, const void* yx, int ld, int d
   else return zi_refuse("rglru_decode: unknown dtype tags %d, %d", dtype, wg_dtype);
 #undef ZI_RGLRU_DECODE
   return zi_check_launch("rglru_decode");
+}
+
+extern "C" long long zi_rglru_chunked_workspace_floats(int T, int C, int n_seqs, int chunk) {
+  const long long n_chunks = (T + chunk - 1) / chunk;
+  return 3 * n_chunks * C + (long long)n_seqs * C;
+}
+
+extern "C" int zi_rglru_scan_chunked(void* out, int ldo, float* work, const float* u, const float* gates, int block_width,
+                                     const float* rb, const float* ib, const float* lam, float decay_scale, const void* y,
+                                     int ldy, const float* yb, const void* x, int ldx, const float* xb, int dtype,
+                                     float* state, int C, int taps, const int* cu_q, const int* state_slots, int n_seqs,
+                                     int T, int chunk, cudaStream_t stream) {
+  if (n_seqs <= 0 || T <= 0) return 0;
+  if (taps < 1 || taps > 9) return zi_refuse("rglru_scan: 1 to 9 taps, got %d", taps);
+  if (chunk < 1) return zi_refuse("rglru_scan: chunks of %d tokens", chunk);
+  if (block_width <= 0 || C % block_width) return zi_refuse("rglru_scan: %d channels do not divide into blocks of %d", C, block_width);
+  const int n_chunks = (T + chunk - 1) / chunk;
+  float* ab = work;                                   // [n_chunks][2][C]
+  float* s_in = work + (size_t)2 * n_chunks * C;      // [n_chunks][C]
+  float* last = s_in + (size_t)n_chunks * C;          // [n_seqs][C]
+  dim3 grid((C + 127) / 128, n_chunks);
+  ZI_DISPATCH_DTYPE(dtype, TT, {
+    zi_launch(rglru_chunk_kernel<TT, false>, dim3(grid), dim3(128), 0, stream, (TT*)out, ldo, ab, (const float*)s_in, last, u,
+              gates, block_width, rb, ib, lam, decay_scale, (const TT*)y, ldy, yb, (const float*)state, C, taps, cu_q,
+              state_slots, n_seqs, T, chunk);
+    zi_launch(rglru_carry_kernel, dim3((C + 127) / 128), dim3(128), 0, stream, s_in, (const float*)ab, C, n_chunks);
+    zi_launch(rglru_chunk_kernel<TT, true>, dim3(grid), dim3(128), 0, stream, (TT*)out, ldo, ab, (const float*)s_in, last, u,
+              gates, block_width, rb, ib, lam, decay_scale, (const TT*)y, ldy, yb, (const float*)state, C, taps, cu_q,
+              state_slots, n_seqs, T, chunk);
+    zi_launch(rglru_finish_kernel<TT>, dim3((C + 127) / 128, n_seqs), dim3(128), 0, stream, state, (const float*)last,
+              (const TT*)x, ldx, xb, C, taps, cu_q, state_slots);
+  });
+  return zi_check_launch("rglru_scan_chunked");
 }
 
 extern "C" int zi_causal_conv(float* u, const void* x, int ldx, int dtype, const float* xb, const float* kern,

@@ -536,6 +536,46 @@ def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int
     return chosen, weight
 
 
+def moe_router(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int,
+               renormalize: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """The router's product (32-bit multiply-adds whatever the operands' types) and :func:`moe_route` in one
+    kernel, one block per token."""
+    T, K = x.shape
+    NR = w_router.shape[0]
+    _need(x.stride(1) == 1 and w_router.is_contiguous() and w_router.shape[1] == K, "moe_router: shapes")
+    if correction is not None:
+        _need(correction.dtype == torch.float32 and correction.numel() == NR, "the correction is float32 [outputs]")
+    chosen = torch.empty((T, top), dtype=torch.int32, device=x.device)
+    weight = torch.empty((T, top), dtype=torch.float32, device=x.device)
+    with _prof.region(f"moe router N={NR} K={K}", lambda: _nb(w_router) + T * K * x.element_size(), 2 * T * NR * K):
+        _check(lib().zi_moe_router(_ptr(chosen), _ptr(weight), _ptr(x), _tag(x), x.stride(0), _ptr(w_router), _tag(w_router),
+                                   _ptr(correction), T, K, NR, top, 1 if renormalize else 0, _stream()), "moe_router")
+    return chosen, weight
+
+
+def linear_few_rows_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether :func:`linear_few_rows` takes these operands: one type, rows in whole 16-byte pieces."""
+    return bool(x.dtype == weight.dtype and x.shape[1] % 4 == 0 and x.stride(0) % 4 == 0 and x.stride(1) == 1
+                and weight.is_contiguous() and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def linear_few_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_src: torch.Tensor,
+                    tile_group: torch.Tensor, n_tiles: torch.Tensor, relu2: bool = False) -> torch.Tensor:
+    """:func:`linear_grouped` for tiles of 16 rows when the rows are few (a decode step): every weight row is
+    streamed once per tile and multiplied with the tile's 16 rows; bound by memory."""
+    G, N, K = weight.shape
+    rows = out.shape[0]
+    _need(rows % MOE_TILE_ROWS_SMALL == 0 and out.shape[1] == N and out.stride(1) == 1, "linear_few_rows: shapes")
+    pairs = max(1, rows - G * MOE_TILE_ROWS_SMALL)
+    with _prof.region(f"linear (grouped, few rows) N={N} K={K}",
+                      lambda: min(G, pairs) * N * K * weight.element_size() + pairs * (K + N) * x.element_size(), 2 * pairs * N * K):
+        _check(lib().zi_moe_few_rows(_ptr(out), _tag(out), out.stride(0), _ptr(x), _tag(x), x.stride(0), _ptr(weight),
+                                     _ptr(_i32(row_src, "row_src")), _ptr(_i32(tile_group, "tile_group")),
+                                     _ptr(_i32(n_tiles, "n_tiles")), rows // MOE_TILE_ROWS_SMALL, N, K, 1 if relu2 else 0,
+                                     _stream()), "linear_few_rows")
+    return out
+
+
 MOE_TILE_ROWS_SMALL, MOE_TILE_ROWS, MOE_TILE_ROWS_TENSOR = 16, 64, 128
 
 
@@ -609,6 +649,9 @@ def moe_combine(y: torch.Tensor, x: torch.Tensor, chosen: torch.Tensor, weight: 
 
 
 # ---------------------------------------------------------------- recurrent mixers
+RGLRU_CHUNK = 32    # tokens per chunk of the chunked recurrence (bfloat16 steps of 128 tokens and more)
+
+
 def causal_conv(x: torch.Tensor, x_bias: torch.Tensor, kernel: torch.Tensor, bias: torch.Tensor, state: torch.Tensor,
                 step) -> torch.Tensor:
     """Per-channel causal convolution of ``x + x_bias`` ([T, C], rows may be views of wider rows) with
@@ -636,13 +679,25 @@ def rglru_scan(u: torch.Tensor, gates: torch.Tensor, block_width: int, r_bias: t
     ``a = exp(-decay_scale * sigmoid(g_r + r_bias) * softplus(lam))``,
     ``S = a S + sqrt(1 - a^2) * sigmoid(g_i + i_bias) * u``; returns ``S * gelu_tanh(y + y_bias)`` in ``y``'s
     type.  ``gates`` float32 [T, blocks, 2, block_width] holds g_r and g_i; ``x`` (the convolution's input
-    before its bias) is read to carry the convolution's last inputs on."""
+    before its bias) is read to carry the convolution's last inputs on.  A bfloat16 step of many tokens
+    runs the recurrence in chunks (the same sums, associated per chunk)."""
     T, C = u.shape
     taps = state.shape[1]
     _need(u.dtype == torch.float32 and gates.dtype == torch.float32 and u.is_contiguous() and gates.is_contiguous()
           and gates.numel() == 2 * T * C, "rglru_scan: u [T, C] and gates [T, 2C] are contiguous float32")
     _need(y.dtype == x.dtype and y.stride(1) == 1 and x.stride(1) == 1, "rglru_scan: branch rows are dense")
     out = torch.empty((T, C), dtype=y.dtype, device=y.device)
+    if y.dtype == torch.bfloat16 and T >= 4 * RGLRU_CHUNK:
+        # a prompt: the recurrence in chunks, so that its tokens do not wait for one another
+        need = lib().zi_rglru_chunked_workspace_floats(T, C, step.n_seqs, RGLRU_CHUNK)
+        work = torch.empty((need,), dtype=torch.float32, device=y.device)
+        with _prof.region("rglru scan (chunks)", lambda: 2 * T * C * (12 + 3 * y.element_size())):
+            _check(lib().zi_rglru_scan_chunked(
+                _ptr(out), out.stride(0), _ptr(work), _ptr(u), _ptr(gates), block_width, _ptr(r_bias), _ptr(i_bias), _ptr(lam),
+                ctypes.c_float(decay_scale), _ptr(y), y.stride(0), _ptr(y_bias), _ptr(x), x.stride(0), _ptr(x_bias), _tag(y),
+                _ptr(state), C, taps, _ptr(step.cu_q), _ptr(step.state_slots), step.n_seqs, T, RGLRU_CHUNK, _stream()),
+                "rglru_scan_chunked")
+        return out
     with _prof.region("rglru scan", lambda: T * C * (12 + 3 * y.element_size())):
         _check(lib().zi_rglru_scan(_ptr(out), out.stride(0), _ptr(u), _ptr(gates), block_width, _ptr(r_bias), _ptr(i_bias),
                                    _ptr(lam), ctypes.c_float(decay_scale), _ptr(y), y.stride(0), _ptr(y_bias), _ptr(x),

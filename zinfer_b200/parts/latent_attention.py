@@ -25,6 +25,7 @@ from .base import KVCacheNeed, Mixer, TensorSpec, make_part
 
 class LatentAttention(Mixer):
     graph_safe = True
+    PER_HEAD_TENSOR_FROM = 128     # tokens in a step from which the per-head products go to the tensor cores
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
@@ -82,8 +83,11 @@ class LatentAttention(Mixer):
 
     # ------------------------------------------------------------------ forward
     def _per_head(self, x, weight, out):
-        """out[:, n] = x[:, n] @ weight[n]^T for every head n (views [T, heads, *])."""
-        if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and ops.tensor_core_linear_ok(x[:, 0], weight[0]):
+        """out[:, n] = x[:, n] @ weight[n]^T for every head n (views [T, heads, *]).  Many tokens in bfloat16: one
+        tensor-core product per head; few tokens (a decode step) and float32: all heads in one launch of the
+        batched CUDA-core product, which is bound by reading the weights once either way."""
+        if x.shape[0] > self.PER_HEAD_TENSOR_FROM and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 \
+                and ops.tensor_core_linear_ok(x[:, 0], weight[0]) and ops.tensor_core_linear_ok(x[:, -1], weight[-1]):
             for n in range(self.heads):
                 ops.linear(x[:, n], weight[n], out=out[:, n])
         else:

@@ -64,8 +64,11 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x):
         T = x.shape[0]
-        logits = ops.linear_cuda_cores(x, self.w_router, out_dtype=torch.float32)     # 32-bit multiply-adds
-        chosen, weight = ops.moe_route(logits, self.correction, self.top, self.renormalize)
+        if self.hidden <= 32768:      # the router's product and the choice in one kernel (the row fits its shared memory)
+            chosen, weight = ops.moe_router(x, self.w_router, self.correction, self.top, self.renormalize)
+        else:
+            logits = ops.linear_cuda_cores(x, self.w_router, out_dtype=torch.float32)     # 32-bit multiply-adds
+            chosen, weight = ops.moe_route(logits, self.correction, self.top, self.renormalize)
         pairs = T * self.top
         if pairs >= self.tensor_core_pairs and x.dtype == torch.bfloat16 and self.experts > 0 \
                 and ops.linear_grouped_tensor_ok(self.w_up) and ops.linear_grouped_tensor_ok(self.w_down):
@@ -84,7 +87,12 @@ class RoutedExperts(FeedForward):
         row_token, row_self, pair_row, tile_expert, n_tiles = ops.moe_align(chosen, self.experts, tile)
         rows = row_token.numel()
         mid = torch.empty((rows, self.inter), dtype=self.ctx.dtype, device=x.device)
-        ops.linear_grouped(x, self.w_up, mid, row_token, tile_expert, n_tiles, tile, relu2=True)
         y = torch.empty((rows, self.hidden), dtype=torch.float32, device=x.device)
-        ops.linear_grouped(mid, self.w_down, y, row_self, tile_expert, n_tiles, tile)
+        if tile == ops.MOE_TILE_ROWS_SMALL and ops.linear_few_rows_ok(x, self.w_up) and ops.linear_few_rows_ok(mid, self.w_down):
+            # few rows per expert (a decode step): the experts' weights are streamed once, bound by memory
+            ops.linear_few_rows(x, self.w_up, mid, row_token, tile_expert, n_tiles, relu2=True)
+            ops.linear_few_rows(mid, self.w_down, y, row_self, tile_expert, n_tiles)
+        else:
+            ops.linear_grouped(x, self.w_up, mid, row_token, tile_expert, n_tiles, tile, relu2=True)
+            ops.linear_grouped(mid, self.w_down, y, row_self, tile_expert, n_tiles, tile)
         return ops.moe_combine(y, x, chosen, weight, pair_row, self.experts)
