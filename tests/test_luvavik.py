@@ -79,6 +79,21 @@ def test_config_is_read_and_registered():
         LuvavikConfig.from_dict(bad)
 
 
+def test_command_line_inspects_the_model(tmp_path):
+    import io
+
+    from zinfer_b200 import cli
+
+    d = U.write_model(str(tmp_path / "m"), U.CONFIGS["alt"], U.make_weights(U.CONFIGS["alt"], seed=1))
+    out = io.StringIO()
+    assert cli.run(["inspect-config", d], out) == 0
+    text = out.getvalue()
+    assert "architecture: Luvavik" in text and "loop: layers 0..1 run 1 times" in text
+    assert "layer 1: latent_attention" in text and "moe experts=4 top=1 identity=0 ff=56" in text
+    out = io.StringIO()
+    assert cli.run(["inspect-weights", d], out) == 0 and "tensor_count:" in out.getvalue()
+
+
 def test_caches_and_states_per_pass():
     from zinfer_b200.config import LuvavikConfig, luvavik_model_spec
     from zinfer_b200.engine import DecoderModel

@@ -175,6 +175,10 @@ def inspect_config(model_dir: str, out) -> None:
     print(f"model_dir: {model_dir}", file=out)
     print(f"model_type: {cfg.model_type}", file=out)
     print(f"architecture: {fam.name}", file=out)
+    if hasattr(cfg, "describe"):       # a family whose configuration is not Qwen3's list of sizes says what it has
+        for line in cfg.describe():
+            print(line, file=out)
+        return
     for k in ("hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads",
               "head_dim", "vocab_size", "max_position_embeddings"):
         print(f"{k}: {getattr(cfg, k)}", file=out)

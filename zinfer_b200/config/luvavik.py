@@ -114,6 +114,25 @@ class LuvavikConfig:
             if not (0 <= self.loop["start"] < self.loop["stop"] <= len(self.layers)) or self.loop["times"] < 1:
                 raise ConfigError(f"config.json: loop {self.loop} does not fit {len(self.layers)} layers")
 
+    def describe(self) -> list[str]:
+        """Lines for the command line's model inspection."""
+        lines = [f"hidden_size: {self.hidden_size}", f"vocab_size: {self.vocab_size}", f"num_layers: {len(self.layers)}",
+                 f"norm_eps: {self.norm_eps:e}", f"residual_mult: {self.residual_mult}", f"logit_scale: {self.logit_scale}"]
+        if self.loop is not None:
+            lines.append(f"loop: layers {self.loop['start']}..{self.loop['stop'] - 1} run {self.loop['times']} times")
+        for i, layer in enumerate(self.layers):
+            mixer = ", ".join(f"{k}={v}" for k, v in sorted(layer["mixer"].items()) if not isinstance(v, dict))
+            mlp = layer.get("mlp")
+            if mlp is None:
+                ff = "none"
+            elif mlp["kind"] == "dense":
+                ff = f"dense ff={mlp['ff']}"
+            else:
+                r = mlp["router"]
+                ff = f"moe experts={r['experts']} top={r['top']} identity={r.get('identity', 0)} ff={mlp['expert']['ff']}"
+            lines.append(f"layer {i}: {layer['type']} ({mixer}); feed-forward: {ff}")
+        return lines
+
     def to_dict(self) -> dict:
         d: dict[str, Any] = {
             "architecture": ARCHITECTURE, "vocab": self.vocab_size, "width": self.hidden_size,

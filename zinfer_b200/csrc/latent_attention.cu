@@ -164,8 +164,9 @@ latent_decode_kernel(T* __restrict__ out, int out_stride, float* __restrict__ wo
   pdl_wait();
   extern __shared__ float sm[];
   float* qs = sm;                              // [LD_HEADS][D]
-  float* ks = qs + LD_HEADS * D;               // [LD_KEYS][D + 1]
-  float* ps = ks + LD_KEYS * (D + 1);          // [LD_HEADS][LD_KEYS]
+  const int KP = D + 4;                        // row pitch of ks: 16-byte accesses, no bank conflicts between rows
+  float* ks = qs + LD_HEADS * D;               // [LD_KEYS][KP]
+  float* ps = ks + LD_KEYS * KP;               // [LD_HEADS][LD_KEYS]
   float* al = ps + LD_HEADS * LD_KEYS;         // [LD_HEADS] rescale of this tile
   const int split = blockIdx.x, seq = dec_seq[blockIdx.y], h0 = blockIdx.z * LD_HEADS;
   const int nh = min(LD_HEADS, heads - h0);
@@ -197,7 +198,7 @@ latent_decode_kernel(T* __restrict__ out, int out_stride, float* __restrict__ wo
     for (int kk = warp; kk < LD_KEYS; kk += LD_THREADS / 32) {      // a warp per cached row: one page lookup
       const int j = k0 + kk;
       const int page = j < kv_len ? bt[j / page_size] : -1;
-      float* dst = ks + kk * (D + 1);
+      float* dst = ks + kk * KP;
       if (page < 0) {
         for (int c = lane; c < D; c += 32) dst[c] = 0.f;
       } else {
@@ -206,11 +207,8 @@ latent_decode_kernel(T* __restrict__ out, int out_stride, float* __restrict__ wo
           for (int c = lane * 8; c < D; c += 256) {
             const uint4 raw = *reinterpret_cast<const uint4*>(row + c);
             const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              dst[c + 2 * i] = __low2float(p2[i]);
-              dst[c + 2 * i + 1] = __high2float(p2[i]);
-            }
+            *reinterpret_cast<float4*>(dst + c) = make_float4(__low2float(p2[0]), __high2float(p2[0]), __low2float(p2[1]), __high2float(p2[1]));
+            *reinterpret_cast<float4*>(dst + c + 4) = make_float4(__low2float(p2[2]), __high2float(p2[2]), __low2float(p2[3]), __high2float(p2[3]));
           }
         } else {
           for (int c = lane; c < D; c += 32) dst[c] = to_f32(row[c]);
@@ -220,13 +218,13 @@ latent_decode_kernel(T* __restrict__ out, int out_stride, float* __restrict__ wo
     __syncthreads();
     float sa = 0.f, sb = 0.f;
     {
-      const float* kr = ks + lane * (D + 1);
-      const float* qa = qs + ha * D;
-      const float* qb = qs + hb * D;
-      for (int c = 0; c < D; ++c) {
-        const float kv = kr[c];
-        sa = fmaf(qa[c], kv, sa);
-        sb = fmaf(qb[c], kv, sb);
+      const float4* kr = reinterpret_cast<const float4*>(ks + lane * KP);
+      const float4* qa = reinterpret_cast<const float4*>(qs + ha * D);
+      const float4* qb = reinterpret_cast<const float4*>(qs + hb * D);
+      for (int c = 0; c < D / 4; ++c) {       // D is a multiple of 4 (checked by the launcher)
+        const float4 kv = kr[c], a4 = qa[c], b4 = qb[c];
+        sa = fmaf(a4.x, kv.x, fmaf(a4.y, kv.y, fmaf(a4.z, kv.z, fmaf(a4.w, kv.w, sa))));
+        sb = fmaf(b4.x, kv.x, fmaf(b4.y, kv.y, fmaf(b4.z, kv.z, fmaf(b4.w, kv.w, sb))));
       }
     }
     const bool live = k0 + lane < kv_len;
@@ -255,7 +253,7 @@ latent_decode_kernel(T* __restrict__ out, int out_stride, float* __restrict__ wo
     for (int kk = 0; kk < LD_KEYS; ++kk) {
       float v[LD_MAXC];
 #pragma unroll
-      for (int j = 0; j < LD_MAXC; ++j) v[j] = col + 128 * j < rank ? ks[kk * (D + 1) + col + 128 * j] : 0.f;
+      for (int j = 0; j < LD_MAXC; ++j) v[j] = col + 128 * j < rank ? ks[kk * KP + col + 128 * j] : 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float p = ps[(hg + i) * LD_KEYS + kk];
@@ -332,7 +330,8 @@ extern "C" int zi_latent_decode(void* out, int out_stride, float* work, const vo
   if (n_dec <= 0) return 0;
   if (rank > 128 * LD_MAXC || rank > D) return zi_refuse("latent_decode: a latent of %d values (rows of %d) is more than this kernel holds", rank, D);
   if (splits < 1 || (splits > 1 && !work)) return zi_refuse("latent_decode: %d splits need a workspace", splits);
-  const size_t smem = (size_t)(LD_HEADS * D + LD_KEYS * (D + 1) + LD_HEADS * LD_KEYS + LD_HEADS) * sizeof(float);
+  if (D % 4) return zi_refuse("latent_decode: rows of %d values are not whole 16-byte pieces", D);
+  const size_t smem = (size_t)(LD_HEADS * D + LD_KEYS * (D + 4) + LD_HEADS * LD_KEYS + LD_HEADS) * sizeof(float);
   dim3 grid(splits, n_dec, (heads + LD_HEADS - 1) / LD_HEADS);
   ZI_DISPATCH_DTYPE(dtype, TT, {
     auto kern = latent_decode_kernel<TT>;

@@ -112,12 +112,12 @@ moe_router_kernel(int* __restrict__ chosen, float* __restrict__ weight, const TX
 }
 
 // Few rows per expert (a decode step): out[r, n] = act(sum_k x[row_src[r], k] * w[e][n][k]) for the rows r of
-// tile `blockIdx.y` (16 rows, one expert e).  A block takes 8 output columns, a warp one: its lanes stream
-// the weight row once in 8-byte pieces and multiply it with all 16 rows, which lie in shared memory as
-// 32-bit values, K_CHUNK columns at a time.  The weights are read once per tile: bound by memory, not by
+// tile `blockIdx.y` (16 rows, one expert e).  A block takes 16 output columns, a warp two: its lanes stream
+// the weight rows once in 8-byte pieces and multiply them with the tile's rows in use (they come first in
+// a tile), which lie in shared memory as 32-bit values, FR_CHUNK columns at a time.  The weights are read once per tile: bound by memory, not by
 // multiply-adds.  Needs K % 4 == 0.  Every output is one sum in a fixed order (lane-strided, then the
 // lanes' partial sums), independent of the batch.
-constexpr int FR_ROWS = 16, FR_COLS = 8, FR_CHUNK = 1024;
+constexpr int FR_ROWS = 16, FR_WARPS = 8, FR_PER_WARP = 2, FR_COLS = FR_WARPS * FR_PER_WARP, FR_CHUNK = 1024;
 
 __device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
@@ -128,7 +128,7 @@ __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
 }
 
 template <typename TX, typename TW, typename TO>
-__global__ void __launch_bounds__(FR_COLS * 32)
+__global__ void __launch_bounds__(FR_WARPS * 32)
 moe_few_rows_kernel(TO* __restrict__ out, int ldo, const TX* __restrict__ x, int ldx, const TW* __restrict__ w,
                     const int* __restrict__ row_src, const int* __restrict__ tile_group,
                     const int* __restrict__ n_tiles_dev, int N, int K, int relu2) {
@@ -137,42 +137,65 @@ moe_few_rows_kernel(TO* __restrict__ out, int ldo, const TX* __restrict__ x, int
   if ((int)blockIdx.y >= *n_tiles_dev) return;
   extern __shared__ float xs[];            // [FR_ROWS][FR_CHUNK]
   __shared__ int src[FR_ROWS];
+  __shared__ int n_used;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r0 = blockIdx.y * FR_ROWS, n = blockIdx.x * FR_COLS + warp;
+  const int r0 = blockIdx.y * FR_ROWS, n0 = blockIdx.x * FR_COLS + warp * FR_PER_WARP;
   if (threadIdx.x < FR_ROWS) src[threadIdx.x] = row_src[r0 + threadIdx.x];
-  const TW* wr = w + ((size_t)tile_group[blockIdx.y] * N + (n < N ? n : 0)) * K;
-  float acc[FR_ROWS];
+  __syncthreads();
+  if (threadIdx.x == 0) {          // the rows in use come first
+    int u = 0;
+    while (u < FR_ROWS && src[u] >= 0) ++u;
+    n_used = u;
+  }
+  __syncthreads();
+  const int used = n_used;
+  if (used == 0) return;
+  const TW* wbase = w + (size_t)tile_group[blockIdx.y] * N * K;
+  const TW* wr[FR_PER_WARP];
 #pragma unroll
-  for (int r = 0; r < FR_ROWS; ++r) acc[r] = 0.f;
+  for (int j = 0; j < FR_PER_WARP; ++j) wr[j] = wbase + (size_t)(n0 + j < N ? n0 + j : 0) * K;
+  float acc[FR_PER_WARP][FR_ROWS];
+#pragma unroll
+  for (int j = 0; j < FR_PER_WARP; ++j)
+#pragma unroll
+    for (int r = 0; r < FR_ROWS; ++r) acc[j][r] = 0.f;
   for (int k0 = 0; k0 < K; k0 += FR_CHUNK) {
     const int kc = min(FR_CHUNK, K - k0);
-    __syncthreads();     // the chunk before is consumed; src is written
-    for (int e = threadIdx.x * 4; e < FR_ROWS * kc; e += blockDim.x * 4) {
+    __syncthreads();     // the chunk before is consumed
+    for (int e = threadIdx.x * 4; e < used * kc; e += blockDim.x * 4) {
       const int r = e / kc, k = e - r * kc;
-      const float4 v = src[r] >= 0 ? load4(x + (size_t)src[r] * ldx + k0 + k) : make_float4(0.f, 0.f, 0.f, 0.f);
-      *reinterpret_cast<float4*>(xs + r * FR_CHUNK + k) = v;
+      *reinterpret_cast<float4*>(xs + r * FR_CHUNK + k) = load4(x + (size_t)src[r] * ldx + k0 + k);
     }
     __syncthreads();
     for (int k = lane * 4; k < kc; k += 128) {
-      const float4 wv = load4(wr + k0 + k);
+      float4 wv[FR_PER_WARP];
+#pragma unroll
+      for (int j = 0; j < FR_PER_WARP; ++j) wv[j] = load4(wr[j] + k0 + k);
 #pragma unroll
       for (int r = 0; r < FR_ROWS; ++r) {
-        const float4 xv = *reinterpret_cast<const float4*>(xs + r * FR_CHUNK + k);
-        acc[r] = fmaf(wv.x, xv.x, fmaf(wv.y, xv.y, fmaf(wv.z, xv.z, fmaf(wv.w, xv.w, acc[r]))));
+        if (r < used) {
+          const float4 xv = *reinterpret_cast<const float4*>(xs + r * FR_CHUNK + k);
+#pragma unroll
+          for (int j = 0; j < FR_PER_WARP; ++j)
+            acc[j][r] = fmaf(wv[j].x, xv.x, fmaf(wv[j].y, xv.y, fmaf(wv[j].z, xv.z, fmaf(wv[j].w, xv.w, acc[j][r]))));
+        }
       }
     }
   }
 #pragma unroll
-  for (int r = 0; r < FR_ROWS; ++r) {
-    float v = warp_sum(acc[r]);
-    if (lane == 0 && n < N && src[r] >= 0) {
-      if (relu2) {
-        v = fmaxf(v, 0.f);
-        v *= v;
+  for (int j = 0; j < FR_PER_WARP; ++j)
+#pragma unroll
+    for (int r = 0; r < FR_ROWS; ++r) {
+      if (r >= used) continue;      // uniform in the block
+      float v = warp_sum(acc[j][r]);
+      if (lane == 0 && n0 + j < N) {
+        if (relu2) {
+          v = fmaxf(v, 0.f);
+          v *= v;
+        }
+        out[(size_t)(r0 + r) * ldo + n0 + j] = from_f32<TO>(v);
       }
-      out[(size_t)(r0 + r) * ldo + n] = from_f32<TO>(v);
     }
-  }
 }
 
 // One block lays the P = T * top pairs out by expert.  Pairs of expert e take the rows
@@ -315,7 +338,7 @@ extern "C" int zi_moe_few_rows(void* out, int out_dtype, int ldo, const void* x,
     auto kern = moe_few_rows_kernel<TX, TX, TO>;                                                                   \
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)         \
       return zi_refuse("moe_few_rows: cannot get %zu bytes of shared memory", smem);                               \
-    zi_launch(kern, dim3(grid), dim3(FR_COLS * 32), smem, stream, (TO*)out, ldo, (const TX*)x, ldx, (const TX*)w, row_src, \
+    zi_launch(kern, dim3(grid), dim3(FR_WARPS * 32), smem, stream, (TO*)out, ldo, (const TX*)x, ldx, (const TX*)w, row_src, \
               tile_group, n_tiles_dev, N, K, relu2);                                                               \
   } while (0)
   if (dtype == ZI_F32 && out_dtype == ZI_F32) ZI_FEW(float, float);

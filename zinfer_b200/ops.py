@@ -779,7 +779,7 @@ def latent_attention(q_eff: torch.Tensor, cache: torch.Tensor, block_tables: tor
     out = torch.empty((T, heads * rank), dtype=q_eff.dtype, device=q_eff.device)
     skip_from = skip_single = 0
     n_dec = int(getattr(step, "n_dec", 0) or 0)
-    if n_dec > 0 and not window and rank <= 640 and ATTENTION_BACKEND != "generic":
+    if n_dec > 0 and not window and rank <= 640 and D % 4 == 0 and ATTENTION_BACKEND != "generic":
         # requests that bring one token: split-key kernel, every cached row fetched once for 16 heads
         splits = latent_decode_splits(n_dec, -(-heads // 16), _sm_count(q_eff.device), step.max_kv_len,
                                       fixed=q_eff.dtype == torch.float32)
