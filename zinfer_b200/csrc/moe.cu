@@ -12,6 +12,15 @@
 namespace {
 constexpr int ROUTE_WARPS = 4;
 
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+
+
 // One warp per token.  Sums run over a fixed order of lanes, so a token's choice does not depend on
 // the batch.  Ties go to the lower index.  z: the token's NR logits; score, pick: NR floats each of
 // shared memory for this warp.
@@ -100,10 +109,19 @@ moe_router_kernel(int* __restrict__ chosen, float* __restrict__ weight, const TX
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f32(x[(size_t)t * ldx + k]);
   __syncthreads();
+  const bool vec = K % 4 == 0 && ((uintptr_t)w & 15) == 0;      // 8- or 16-byte pieces of a weight row
   for (int j = warp; j < NR; j += 4) {
     const TW* wr = w + (size_t)j * K;
     float acc = 0.f;
-    for (int k = lane; k < K; k += 32) acc = fmaf(xs[k], to_f32(wr[k]), acc);
+    if (vec) {
+      for (int k = lane * 4; k < K; k += 128) {
+        const float4 wv = load4(wr + k);
+        const float4 xv = *reinterpret_cast<const float4*>(xs + k);
+        acc = fmaf(xv.x, wv.x, fmaf(xv.y, wv.y, fmaf(xv.z, wv.z, fmaf(xv.w, wv.w, acc))));
+      }
+    } else {
+      for (int k = lane; k < K; k += 32) acc = fmaf(xs[k], to_f32(wr[k]), acc);
+    }
     acc = warp_sum(acc);
     if (lane == 0) z[j] = acc;
   }
@@ -118,14 +136,6 @@ moe_router_kernel(int* __restrict__ chosen, float* __restrict__ weight, const TX
 // multiply-adds.  Needs K % 4 == 0.  Every output is one sum in a fixed order (lane-strided, then the
 // lanes' partial sums), independent of the batch.
 constexpr int FR_ROWS = 16, FR_WARPS = 8, FR_PER_WARP = 2, FR_COLS = FR_WARPS * FR_PER_WARP, FR_CHUNK = 1024;
-
-__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
-__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
-  const uint2 raw = *reinterpret_cast<const uint2*>(p);
-  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
-}
 
 template <typename TX, typename TW, typename TO>
 __global__ void __launch_bounds__(FR_WARPS * 32)
