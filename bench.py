@@ -19,6 +19,12 @@ for every request).  Prints ONE JSON line:
             requests' cache) / time, against the measured copy bandwidth
   points    decode tokens/s at batch 1 and 64
 
+With ``--design luvavik`` it runs another measurement instead and prints a JSON line of its own: prefill
+(2,048 tokens) and decode (batch 8, 2,048 cached tokens each) throughput of the Luvavik design at layer
+sizes of real models (widths 2048 and 4096; ``--design-sizes``), beside Qwen3 dense at the same width,
+layer count and multiply-adds per token; ``--profile PATH`` adds both models' per-kernel-class times and
+roofline fractions.  The default workload and its contract are untouched.
+
 Peaks come from MEASURED_PEAKS.json when the driver wrote it, else the fallback
 figures (6.65 TB/s, 1.59 PFLOP/s).  Weights (15 GB) exceed L2 (126 MB), so every
 step streams its inputs from HBM without a flush.  For --gpus > 1 it says that
