@@ -23,7 +23,7 @@ With ``--design luvavik`` it runs another measurement instead and prints a JSON 
 (2,048 tokens) and decode (batch 8, 2,048 cached tokens each) throughput of the Luvavik design at layer
 sizes of real models (widths 2048 and 4096; ``--design-sizes``), beside Qwen3 dense at the same width,
 layer count and multiply-adds per token; ``--profile PATH`` adds both models' per-kernel-class times and
-roofline fractions.  The default workload and its contract are untouched.
+roofline fractions.  The default workload and its output line are untouched.
 
 Peaks come from MEASURED_PEAKS.json when the driver wrote it, else the fallback
 figures (6.65 TB/s, 1.59 PFLOP/s).  Weights (15 GB) exceed L2 (126 MB), so every

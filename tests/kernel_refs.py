@@ -75,8 +75,8 @@ def interleave_gate_up(gate, up, block=64):
     return torch.stack([gate.view(I // block, block, K), up.view(I // block, block, K)], dim=1).reshape(2 * I, K).contiguous()
 
 
-def linear_swiglu(x, w_interleaved, out_dtype=None):
-    return swiglu(linear(x, w_interleaved, out_dtype=torch.float32), interleave=64).to(out_dtype or x.dtype)
+def linear_swiglu(x, w_interleaved, out_dtype=None, activation="silu"):
+    return swiglu(linear(x, w_interleaved, out_dtype=torch.float32), interleave=64, activation=activation).to(out_dtype or x.dtype)
 
 
 def swiglu(gate_up, out=None, out_dtype=None, interleave=0, activation="silu"):

@@ -239,6 +239,12 @@ def test_linear_swiglu_fused_epilogue(M, I, K):
     # the unfused route (product, then the SwiGLU kernel on the interleaved columns) agrees
     unfused = o.swiglu(o.linear(x, w), interleave=64)
     torch.testing.assert_close(unfused.float(), want, rtol=2e-2, atol=2e-3 * K ** 0.5 * 0.05 + 2e-3)
+    # the same epilogue with the tanh form of gelu on the gate
+    want = ref.gelu_tanh(g) * u
+    got = o.linear_swiglu(x, w, activation="gelu_tanh")
+    torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=2e-3 * K ** 0.5 * 0.05 + 1e-3)
+    unfused = o.swiglu(o.linear(x, w), interleave=64, activation="gelu_tanh")
+    torch.testing.assert_close(unfused.float(), want, rtol=2e-2, atol=2e-3 * K ** 0.5 * 0.05 + 2e-3)
     assert o.kernel_status() == 0
 
 

@@ -37,6 +37,8 @@ int zi_swiglu_partials(void* out, int dtype, const float* partials, int splits, 
                        int interleave, cudaStream_t stream);
 int zi_gemm_tcgen05_swiglu(void* out, int out_dtype, const void* x, const void* w, int M, int N2, int K, int ldx,
                            int ldw, int ldo, int sm_count, cudaStream_t stream);
+int zi_gemm_tcgen05_gated(void* out, int out_dtype, const void* x, const void* w, int M, int N2, int K, int ldx,
+                          int ldw, int ldo, int act, int sm_count, cudaStream_t stream);
 int zi_gemm_argmax_units(int N);
 int zi_gemm_tcgen05_argmax(float* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldw, int ldo,
                            float* cand_val, int* cand_idx, int sm_count, cudaStream_t stream);

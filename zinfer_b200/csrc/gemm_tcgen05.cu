@@ -63,11 +63,15 @@ struct GemmArgs {
   int relu2;                 // plain epilogue: the square of relu before the store
   int late_weights;          // the weight-side operand is written by a kernel of this step: nothing is
                              // requested before the wait for the kernels before this one
+  int act;                   // gated epilogue: ZI_ACT_SILU or ZI_ACT_GELU_TANH
 };
 
 constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2;
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+// act(gate) * up: silu, or the tanh form of gelu (ZI_ACT_GELU_TANH); the choice is uniform over a launch
+__device__ __forceinline__ float gated_mul(int act, float g, float u) {
+  return (act == ZI_ACT_GELU_TANH ? gelu_tanh_f32(g) : g / (1.0f + expf(-g))) * u;
+}
 
 // One thread's row of an accumulator (TMEM lane `lane_base`, BN columns) to memory: row `a` of the A
 // side against B rows b_tile * BN ...  `a_ok` is false for rows past the end (the thread still
@@ -92,16 +96,16 @@ __device__ __forceinline__ void drain_accumulator(const GemmArgs& g, TO* __restr
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             uint4 w;
-            w.x = pack2(silu_mul(gv[j], uv[j]), silu_mul(gv[j + 1], uv[j + 1]));
-            w.y = pack2(silu_mul(gv[j + 2], uv[j + 2]), silu_mul(gv[j + 3], uv[j + 3]));
-            w.z = pack2(silu_mul(gv[j + 4], uv[j + 4]), silu_mul(gv[j + 5], uv[j + 5]));
-            w.w = pack2(silu_mul(gv[j + 6], uv[j + 6]), silu_mul(gv[j + 7], uv[j + 7]));
+            w.x = pack2(gated_mul(g.act, gv[j], uv[j]), gated_mul(g.act, gv[j + 1], uv[j + 1]));
+            w.y = pack2(gated_mul(g.act, gv[j + 2], uv[j + 2]), gated_mul(g.act, gv[j + 3], uv[j + 3]));
+            w.z = pack2(gated_mul(g.act, gv[j + 4], uv[j + 4]), gated_mul(g.act, gv[j + 5], uv[j + 5]));
+            w.w = pack2(gated_mul(g.act, gv[j + 6], uv[j + 6]), gated_mul(g.act, gv[j + 7], uv[j + 7]));
             *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(o) + j) = w;
           }
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (f0 + j < g.b_rows / 2) o[j] = from_f32<TO>(silu_mul(gv[j], uv[j]));
+            if (f0 + j < g.b_rows / 2) o[j] = from_f32<TO>(gated_mul(g.act, gv[j], uv[j]));
         }
       }
     }
@@ -799,13 +803,14 @@ int launch_single(void* out, const CUtensorMap& map_a, const CUtensorMap& map_b,
 int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtensorMap& map_b, int M, int N, int K,
                 int ldo, const int* plan, float* partial_buf, int* status, int sm_count, int defer_reduce,
                 const char* what, cudaStream_t stream, int epi = EPI_PLAIN, float* cand_val = nullptr,
-                int* cand_idx = nullptr, const int* tile_group = nullptr, int relu2 = 0) {
+                int* cand_idx = nullptr, const int* tile_group = nullptr, int relu2 = 0, int act = ZI_ACT_SILU) {
   const int swap = plan[0], BN = plan[1], splits = plan[2];
   const int swiglu = epi == EPI_SWIGLU;
   GemmArgs g;
   g.tile_group = tile_group;
   g.group_rows = N;
   g.relu2 = relu2;
+  g.act = act;
   g.late_weights = (defer_reduce >> 1) & 1;
   defer_reduce &= 1;
   g.cand_val = cand_val;
@@ -918,7 +923,14 @@ extern "C" int zi_gemm_tcgen05_grouped(void* out, int out_dtype, const void* x, 
 // plain product and the separate SwiGLU kernel.
 extern "C" int zi_gemm_tcgen05_swiglu(void* out, int out_dtype, const void* x, const void* w, int M, int N2, int K,
                                       int ldx, int ldw, int ldo, int sm_count, cudaStream_t stream) {
+  return zi_gemm_tcgen05_gated(out, out_dtype, x, w, M, N2, K, ldx, ldw, ldo, ZI_ACT_SILU, sm_count, stream);
+}
+
+// The same with the activation of the gate chosen: ZI_ACT_SILU or ZI_ACT_GELU_TANH.
+extern "C" int zi_gemm_tcgen05_gated(void* out, int out_dtype, const void* x, const void* w, int M, int N2, int K,
+                                     int ldx, int ldw, int ldo, int act, int sm_count, cudaStream_t stream) {
   if (M <= 0 || N2 <= 0) return 0;
+  if (act != ZI_ACT_SILU && act != ZI_ACT_GELU_TANH) return zi_refuse("gemm_swiglu: unknown activation tag %d", act);
   if (N2 % 128) return zi_refuse("gemm_swiglu: the interleaved weight needs a multiple of 128 rows, got %d", N2);
   if (!zi_gemm_tcgen05_supported(x, w, K, ldx, ldw))
     return zi_refuse("gemm_swiglu: operands must be 16-byte aligned bfloat16 with row pitches in multiples of 8");
@@ -939,7 +951,7 @@ extern "C" int zi_gemm_tcgen05_swiglu(void* out, int out_dtype, const void* x, c
   int* status = status_word();
   if (!status) return zi_refuse("gemm_swiglu: cannot allocate the status word");
   return launch_gemm(out, out_dtype, map_a, map_b, M, N2, K, ldo, plan, nullptr, status, sm_count, 0, "gemm_swiglu",
-                     stream, EPI_SWIGLU);
+                     stream, EPI_SWIGLU, nullptr, nullptr, nullptr, 0, act);
 }
 
 // Rows of candidates per token that zi_gemm_tcgen05_argmax leaves: one per 32 weight rows,

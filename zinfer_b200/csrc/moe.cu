@@ -97,7 +97,7 @@ moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, const flo
 // memory as 32-bit values, a warp per router output (lanes stride over the row, partial sums meet in a
 // fixed order), then the first warp chooses.  32-bit multiply-adds whatever the operands' types.
 template <typename TX, typename TW>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_router_kernel(int* __restrict__ chosen, float* __restrict__ weight, const TX* __restrict__ x, int ldx,
                   const TW* __restrict__ w, const float* __restrict__ correction, int K, int NR, int top,
                   int renormalize) {
@@ -110,15 +110,29 @@ moe_router_kernel(int* __restrict__ chosen, float* __restrict__ weight, const TX
   for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f32(x[(size_t)t * ldx + k]);
   __syncthreads();
   const bool vec = K % 4 == 0 && ((uintptr_t)w & 15) == 0;      // 8- or 16-byte pieces of a weight row
-  for (int j = warp; j < NR; j += 4) {
+  for (int j = warp; j < NR; j += 8) {
     const TW* wr = w + (size_t)j * K;
     float acc = 0.f;
     if (vec) {
-      for (int k = lane * 4; k < K; k += 128) {
+      // four pieces of the row in flight per lane; the four partial sums meet in a fixed order
+      float part[4] = {0.f, 0.f, 0.f, 0.f};
+      int k = lane * 4;
+      for (; k + 384 < K; k += 512) {
+        float4 wv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) wv[i] = load4(wr + k + 128 * i);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float4 xv = *reinterpret_cast<const float4*>(xs + k + 128 * i);
+          part[i] = fmaf(xv.x, wv[i].x, fmaf(xv.y, wv[i].y, fmaf(xv.z, wv[i].z, fmaf(xv.w, wv[i].w, part[i]))));
+        }
+      }
+      for (; k < K; k += 128) {
         const float4 wv = load4(wr + k);
         const float4 xv = *reinterpret_cast<const float4*>(xs + k);
-        acc = fmaf(xv.x, wv.x, fmaf(xv.y, wv.y, fmaf(xv.z, wv.z, fmaf(xv.w, wv.w, acc))));
+        part[0] = fmaf(xv.x, wv.x, fmaf(xv.y, wv.y, fmaf(xv.z, wv.z, fmaf(xv.w, wv.w, part[0]))));
       }
+      acc = (part[0] + part[1]) + (part[2] + part[3]);
     } else {
       for (int k = lane; k < K; k += 32) acc = fmaf(xs[k], to_f32(wr[k]), acc);
     }
@@ -320,7 +334,7 @@ extern "C" int zi_moe_router(int* chosen, float* weight, const void* x, int x_dt
     auto kern = moe_router_kernel<TX, TW>;                                                                         \
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
       return zi_refuse("moe_router: cannot get %zu bytes of shared memory", smem);                                 \
-    zi_launch(kern, dim3(T), dim3(128), smem, stream, chosen, weight, (const TX*)x, ldx, (const TW*)w, correction, K, NR, \
+    zi_launch(kern, dim3(T), dim3(256), smem, stream, chosen, weight, (const TX*)x, ldx, (const TW*)w, correction, K, NR, \
               top, renormalize);                                                                                   \
   } while (0)
   if (x_dtype == ZI_F32 && w_dtype == ZI_F32) ZI_ROUTER(float, float);

@@ -295,10 +295,12 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int = SWIGLU
     return torch.stack([gate.view(I // block, block, K), up.view(I // block, block, K)], dim=1).reshape(2 * I, K).contiguous()
 
 
-def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """``silu(x Wg^T) * (x Wu^T)`` for a gate/up weight interleaved by :func:`interleave_gate_up`.
-    On the tensor-core path without a K split the SwiGLU runs in the product's epilogue;
-    otherwise the product is followed by the SwiGLU kernel."""
+def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                  activation: str = "silu") -> torch.Tensor:
+    """``act(x Wg^T) * (x Wu^T)`` for a gate/up weight interleaved by :func:`interleave_gate_up`; ``activation``
+    silu (SwiGLU) or gelu_tanh.  On the tensor-core path without a K split the gate runs in the product's
+    epilogue; otherwise the product is followed by the gate's kernel."""
+    _need(activation in ACTIVATIONS, f"unknown activation {activation!r}")
     M, K = x.shape
     N2 = w_interleaved.shape[0]
     if (GEMM_BACKEND != "simt" and x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and M > 0
@@ -306,14 +308,15 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: Optio
             and lib().zi_gemm_tcgen05_supported(_ptr(x), _ptr(w_interleaved), K, x.stride(0), w_interleaved.stride(0))):
         out = torch.empty((M, N2 // 2), dtype=out_dtype or x.dtype, device=x.device)
         with _prof.region(f"linear+swiglu N={N2} K={K}", lambda: _nb(w_interleaved, out) + M * K * 2, 2 * M * N2 * K) as rec:
-            code = lib().zi_gemm_tcgen05_swiglu(_ptr(out), _tag(out), _ptr(x), _ptr(w_interleaved), M, N2, K, x.stride(0),
-                                                w_interleaved.stride(0), out.stride(0), _sm_count(x.device), _stream())
+            code = lib().zi_gemm_tcgen05_gated(_ptr(out), _tag(out), _ptr(x), _ptr(w_interleaved), M, N2, K, x.stride(0),
+                                               w_interleaved.stride(0), out.stride(0), ACTIVATIONS[activation],
+                                               _sm_count(x.device), _stream())
             rec["keep"] = code != -2      # -2: this shape is better served by the product followed by the SwiGLU kernel
         if code != -2:
             _check(code, "linear_swiglu")
             return out
     gu = linear(x, w_interleaved, out_dtype=out_dtype or x.dtype, allow_partials=True)
-    return swiglu(gu, out_dtype=out_dtype or x.dtype, interleave=SWIGLU_INTERLEAVE)
+    return swiglu(gu, out_dtype=out_dtype or x.dtype, interleave=SWIGLU_INTERLEAVE, activation=activation)
 
 
 def rope_table(n_pos: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:

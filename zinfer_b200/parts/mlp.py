@@ -42,11 +42,10 @@ class SwiGLUMLP(FeedForward):
         self.w_down = tensors[self.names[2]].contiguous()
 
     def forward(self, x):
-        if self.interleaved and self.activation == "silu":
-            act = ops.linear_swiglu(x, self.w_gate_up, out_dtype=self.ctx.dtype)
-        else:    # the product's fused epilogue knows silu only
+        if self.interleaved:
+            act = ops.linear_swiglu(x, self.w_gate_up, out_dtype=self.ctx.dtype, activation=self.activation)
+        else:
             gu = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype, allow_partials=True)
-            act = ops.swiglu(gu, out_dtype=self.ctx.dtype, activation=self.activation,
-                             interleave=ops.SWIGLU_INTERLEAVE if self.interleaved else 0)
+            act = ops.swiglu(gu, out_dtype=self.ctx.dtype, activation=self.activation)
         # the product may come back as split-K partial sums; the next norm adds them with the residual
         return ops.linear(act, self.w_down, out_dtype=self.ctx.dtype, allow_partials=True)
