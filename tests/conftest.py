@@ -75,7 +75,7 @@ def cpu_kernels(monkeypatch):
 
     for name in ("embed_gather", "add_rmsnorm", "residual_add", "swiglu", "rope_table", "qk_norm_rope_store",
                  "linear", "attention_tile_rows", "attention_prefill_tile_rows", "paged_attention", "attention", "argmax", "linear_argmax", "patch_tokens", "linear_swiglu", "interleave_gate_up", "decode_fused_ok", "sample", "count_tokens",
-                 "Scaled", "scale_", "sigmoid_gate", "linear_cuda_cores", "tensor_core_linear_ok", "linear_batched",
+                 "Scaled", "scale_", "sigmoid_gate", "linear_cuda_cores", "tensor_core_linear_ok", "linear_batched", "linear_heads_ok",
                  "linear_grouped", "linear_grouped_tensor_ok", "moe_router", "linear_few_rows_ok", "gather_rows", "moe_route", "moe_align", "moe_combine", "causal_conv", "rglru_scan", "rglru_decode", "latent_prepare",
                  "latent_attention"):
         monkeypatch.setattr(ops, name, getattr(kernel_refs, name))

@@ -470,3 +470,24 @@ def test_latent_attention_kernels_agree(dtype, heads, D, rank, page):
             ops.ATTENTION_BACKEND = before
         got = ops.latent_attention(qp, cache, pages, pstep, heads, rank, page, None, 1.0)
         torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+
+
+@gpu
+@pytest.mark.parametrize("T,H,K,N,pitch", [(300, 5, 72, 40, 96), (2048, 16, 128, 512, 192), (129, 3, 512, 128, 512), (200, 1, 64, 24, 80)])
+def test_one_product_per_head_in_one_launch(T, H, K, N, pitch):
+    """The tensor-core kernel's per-head form (heads side by side in their rows, also with columns between them and
+    with K no multiple of the kernel's 64-column blocks) against one 64-bit product per head."""
+    from zinfer_b200 import ops
+
+    gen = torch.Generator().manual_seed(T + H)
+    rows = torch.randn(T, H * pitch + 16, generator=gen).to(torch.bfloat16).to(DEV)
+    x = rows[:, :H * pitch].view(T, H, pitch)[:, :, :K]
+    w = (torch.randn(H, N, K, generator=gen) / K ** 0.5).to(torch.bfloat16).to(DEV)
+    wide = torch.zeros(T, H * (N + 8), dtype=torch.bfloat16, device=DEV)
+    out = wide.view(T, H, N + 8)[:, :, :N]
+    assert ops.linear_heads_ok(x, w, out)
+    ops.linear_heads(x, w, out)
+    want = torch.einsum("thk,hnk->thn", x.double(), w.double())
+    torch.testing.assert_close(out.double(), want, rtol=1e-2, atol=1e-2)
+    assert wide.view(T, H, N + 8)[:, :, N:].abs().max() == 0          # nothing is written between the heads' results
+    ops.require_kernel_status_ok("per-head product")

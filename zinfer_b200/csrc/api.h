@@ -91,6 +91,9 @@ int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const void* w, int 
 int zi_gemm_tcgen05_grouped(void* out, int out_dtype, const void* x, const void* w, int rows, int N, int K, int ldx,
                             int ldw, int ldo, int groups, const int* tile_group, int relu2, int sm_count,
                             cudaStream_t stream);
+// One tensor-core product per head in one launch (activations and results of the heads side by side in their rows).
+int zi_gemm_tcgen05_heads(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K, int ldx, int ldw,
+                          int ldo, int groups, int x_group_cols, int out_group_cols, int sm_count, cudaStream_t stream);
 int zi_gemm_tcgen05_status();
 int zi_gemm_tcgen05_pair_enable(int on);
 

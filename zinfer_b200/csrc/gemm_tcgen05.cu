@@ -64,6 +64,12 @@ struct GemmArgs {
   int late_weights;          // the weight-side operand is written by a kernel of this step: nothing is
                              // requested before the wait for the kernels before this one
   int act;                   // gated epilogue: ZI_ACT_SILU or ZI_ACT_GELU_TANH
+  // Strided groups (one product per head in one launch; tokens on the lanes): the a_tiles are `group_tiles`
+  // tiles of token rows for each group in turn; group n reads its activations a_group_cols columns further
+  // right in the same rows, its weights group_rows rows further down the stack, and writes its results
+  // out_group_stride elements further on.  a_rows then counts the rows of one group.
+  int group_tiles, a_group_cols;
+  long long out_group_stride;
 };
 
 constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2;
@@ -273,7 +279,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (which != 0 && g.weights_once) {
           tma_load_2d_hint(dst, &map_a, &full[s], (kb0 + i) * BLOCK_K, a_tile * TILE_A, once);
         } else {
-          int b_row = b_tile * BN;
+          int b_row = b_tile * BN, a_row = a_tile * TILE_A, a_col = (kb0 + i) * BLOCK_K;
           if (g.tile_group && !use_a) {
             if (group_tile != a_tile) {
               group_tile = a_tile;
@@ -281,8 +287,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             b_row += group_row0;
           }
-          tma_load_2d(use_a ? dst : dst + A_TILE_BYTES, use_a ? &map_a : &map_b, &full[s], (kb0 + i) * BLOCK_K,
-                      use_a ? a_tile * TILE_A : b_row);
+          if (g.group_tiles) {
+            const int grp = a_tile / g.group_tiles;
+            a_row = (a_tile - grp * g.group_tiles) * TILE_A;
+            a_col += grp * g.a_group_cols;
+            b_row += grp * g.group_rows;
+          }
+          tma_load_2d(use_a ? dst : dst + A_TILE_BYTES, use_a ? &map_a : &map_b, &full[s], use_a ? a_col : (kb0 + i) * BLOCK_K,
+                      use_a ? a_row : b_row);
         }
       };
       if (lane < pre) {
@@ -352,10 +364,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const uint32_t acc = lt & 1u, acc_phase = (lt >> 1) & 1u;
       if (!mbar_wait(&accum_full[acc], acc_phase)) { failed = true; atomicExch(status, 3); break; }
       tcgen05_fence_after();
-      const int a = a_tile * TILE_A + quarter * 32 + lane;
+      int a = a_tile * TILE_A + quarter * 32 + lane;
+      TO* out_tile = out;
+      if (g.group_tiles) {      // the row within its group, and the group's place in the output
+        const int grp = a_tile / g.group_tiles;
+        a -= grp * g.group_tiles * TILE_A;
+        out_tile = out + (long long)grp * g.out_group_stride;
+      }
       const uint32_t lane_base = tmem_base + acc * (uint32_t)g.acc_cols + ((uint32_t)(quarter * 32) << 16);
       const bool a_ok = a < g.a_rows;
-      drain_accumulator<TO, EPI>(g, out, partial, split, a, a_ok, b_tile, lane_base);
+      drain_accumulator<TO, EPI>(g, out_tile, partial, split, a, a_ok, b_tile, lane_base);
       // this accumulator may be overwritten by the MMAs of the tile after next
       tcgen05_fence_before();
       __syncwarp();
@@ -803,7 +821,8 @@ int launch_single(void* out, const CUtensorMap& map_a, const CUtensorMap& map_b,
 int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtensorMap& map_b, int M, int N, int K,
                 int ldo, const int* plan, float* partial_buf, int* status, int sm_count, int defer_reduce,
                 const char* what, cudaStream_t stream, int epi = EPI_PLAIN, float* cand_val = nullptr,
-                int* cand_idx = nullptr, const int* tile_group = nullptr, int relu2 = 0, int act = ZI_ACT_SILU) {
+                int* cand_idx = nullptr, const int* tile_group = nullptr, int relu2 = 0, int act = ZI_ACT_SILU,
+                int head_groups = 0, int a_group_cols = 0, long long out_group_stride = 0) {
   const int swap = plan[0], BN = plan[1], splits = plan[2];
   const int swiglu = epi == EPI_SWIGLU;
   GemmArgs g;
@@ -811,6 +830,9 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
   g.group_rows = N;
   g.relu2 = relu2;
   g.act = act;
+  g.group_tiles = 0;
+  g.a_group_cols = a_group_cols;
+  g.out_group_stride = out_group_stride;
   g.late_weights = (defer_reduce >> 1) & 1;
   defer_reduce &= 1;
   g.cand_val = cand_val;
@@ -839,13 +861,19 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
   // few tokens: as many stages (up to 6) as still let two CTAs share an SM's shared memory
   g.stages = swap ? (111 * 1024 / stage_bytes > 6 ? 6 : 111 * 1024 / stage_bytes) : (BN >= 256 ? 4 : 6);
   if (g.stages > g.k_blocks_per_split) g.stages = g.k_blocks_per_split < 2 ? 2 : g.k_blocks_per_split;
+  if (head_groups > 0) {
+    if (swap || g.splits != 1 || epi != EPI_PLAIN || tile_group)
+      return zi_refuse("%s: the product per head runs unsplit with the tokens on the lanes", what);
+    g.group_tiles = g.a_tiles;              // tiles of one group's rows
+    g.a_tiles *= head_groups;
+  }
   const size_t smem = 1024 + (size_t)g.stages * stage_bytes + (2 * g.stages + 4) * sizeof(uint64_t) + 16;
   const int total_tiles = g.a_tiles * g.b_tiles * g.splits;
   float* partial = g.splits > 1 ? partial_buf : nullptr;
 
   if (tile_group && (swap || g.splits != 1 || epi != EPI_PLAIN))
     return zi_refuse("%s: the grouped product runs unsplit with the tokens on the lanes", what);
-  if (!tile_group && use_pair_kernel(plan, M)) {
+  if (!tile_group && !head_groups && use_pair_kernel(plan, M)) {
     ZI_DISPATCH_DTYPE(out_dtype, TO, { return launch_pair<TO>(out, map_a, map_b, g, M, N, K, status, swiglu, what, stream); });
   }
   if (epi == EPI_ARGMAX) {
@@ -915,6 +943,28 @@ extern "C" int zi_gemm_tcgen05_grouped(void* out, int out_dtype, const void* x, 
   if (!status) return zi_refuse("gemm_grouped: cannot allocate the status word");
   return launch_gemm(out, out_dtype, map_a, map_b, rows, N, K, ldo, plan, nullptr, status, sm_count, 0, "gemm_grouped",
                      stream, EPI_PLAIN, nullptr, nullptr, tile_group, relu2);
+}
+
+// One product per head in one launch: out[t, n, :] = x[t, n, :K] * w[n]^T for heads n < groups, where head n's
+// activations lie x_group_cols columns to the right of head n-1's in the same rows of x (row pitch ldx), the
+// weights are stacked [groups * N, K], and head n's results lie out_group_cols columns to the right of head
+// n-1's (row pitch ldo).  Columns of x past a head's K are read and meet zeros of the weight.
+extern "C" int zi_gemm_tcgen05_heads(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K, int ldx,
+                                     int ldw, int ldo, int groups, int x_group_cols, int out_group_cols, int sm_count,
+                                     cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || groups <= 0) return 0;
+  if (!zi_gemm_tcgen05_supported(x, w, K, ldx, ldw) || x_group_cols % 8)
+    return zi_refuse("gemm_heads: operands must be 16-byte aligned bfloat16 with pitches in multiples of 8");
+  const long long cols = (long long)(groups - 1) * x_group_cols + K;
+  if (cols > ldx) return zi_refuse("gemm_heads: %d heads of %d columns do not fit rows of %d", groups, x_group_cols, ldx);
+  int plan[3] = {0, N >= 256 ? 256 : (N >= 128 ? 128 : round_up_bn(N)), 1};
+  CUtensorMap map_a, map_b;
+  if (!make_map(&map_a, x, M, (int)cols, ldx, TILE_A) || !make_map(&map_b, w, groups * N, K, ldw, plan[1]))
+    return zi_refuse("gemm_heads: cuTensorMapEncodeTiled failed");
+  int* status = status_word();
+  if (!status) return zi_refuse("gemm_heads: cannot allocate the status word");
+  return launch_gemm(out, out_dtype, map_a, map_b, M, N, K, ldo, plan, nullptr, status, sm_count, 0, "gemm_heads", stream,
+                     EPI_PLAIN, nullptr, nullptr, nullptr, 0, ZI_ACT_SILU, groups, x_group_cols, out_group_cols);
 }
 
 // gate_up product with the SwiGLU applied in the epilogue: w is [2I, K] with rows interleaved

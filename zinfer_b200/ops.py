@@ -478,6 +478,28 @@ def _ll(v: int):
     return ctypes.c_longlong(int(v))
 
 
+def linear_heads_ok(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bool:
+    """Whether :func:`linear_heads` takes these views: bfloat16, heads side by side in rows that meet TMA's rules."""
+    return bool(GEMM_BACKEND != "simt" and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+                and out.dtype in (torch.bfloat16, torch.float32) and weight.is_contiguous()
+                and x.stride(2) == 1 and out.stride(2) == 1 and x.stride(1) % 8 == 0 and x.stride(0) % 8 == 0
+                and (x.shape[1] - 1) * x.stride(1) + x.shape[2] <= x.stride(0)
+                and lib().zi_gemm_tcgen05_supported(_ptr(x), _ptr(weight), x.shape[2], x.stride(0), weight.shape[2]))
+
+
+def linear_heads(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[:, n] = x[:, n] @ weight[n]^T`` for every head n in ONE launch of the tcgen05 kernel: ``x`` [T, heads, K]
+    and ``out`` [T, heads, N] are views whose heads lie side by side in their rows, ``weight`` [heads, N, K]."""
+    T, H, K = x.shape
+    N = weight.shape[1]
+    _need(weight.shape == (H, N, K) and out.shape == (T, H, N), "linear_heads: shapes")
+    with _prof.region(f"linear (per head, tcgen05) heads={H} N={N} K={K}", lambda: _nb(weight) + T * H * (K + N) * 2,
+                      2 * T * H * N * K):
+        _check(lib().zi_gemm_tcgen05_heads(_ptr(out), _tag(out), _ptr(x), _ptr(weight), T, N, K, x.stride(0), K, out.stride(0),
+                                           H, x.stride(1), out.stride(1), _sm_count(x.device), _stream()), "linear_heads")
+    return out
+
+
 def linear_batched(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
                    relu2: bool = False) -> torch.Tensor:
     """``batch`` independent products ``out[b] = x[b] @ weight[b]^T`` (+ ``bias[b]``) on the CUDA cores with

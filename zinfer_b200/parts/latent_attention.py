@@ -83,9 +83,12 @@ class LatentAttention(Mixer):
 
     # ------------------------------------------------------------------ forward
     def _per_head(self, x, weight, out):
-        """out[:, n] = x[:, n] @ weight[n]^T for every head n (views [T, heads, *]).  Many tokens in bfloat16: one
-        tensor-core product per head; few tokens (a decode step) and float32: all heads in one launch of the
+        """out[:, n] = x[:, n] @ weight[n]^T for every head n (views [T, heads, *]).  Many tokens in bfloat16: the
+        tensor-core kernel's form with one product per head in one launch (or, where the views do not meet its
+        rules, one launch per head); few tokens (a decode step) and float32: all heads in one launch of the
         batched CUDA-core product, which is bound by reading the weights once either way."""
+        if x.shape[0] > self.PER_HEAD_TENSOR_FROM and ops.linear_heads_ok(x, weight, out):
+            return ops.linear_heads(x, weight, out)       # all heads in one launch
         if x.shape[0] > self.PER_HEAD_TENSOR_FROM and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 \
                 and ops.tensor_core_linear_ok(x[:, 0], weight[0]) and ops.tensor_core_linear_ok(x[:, -1], weight[-1]):
             for n in range(self.heads):
