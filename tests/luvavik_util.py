@@ -17,10 +17,10 @@ import torch
 import plain_luvavik as P
 
 
-def attn(heads, dim, rot_dim, vdim, rank, scale, base=10000.0):
+def attn(heads, dim, rot_dim, vdim, rank, scale, base=10000.0, rot_dims=None):
     return {"type": "latent_attention",
             "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": rank, "scale": scale,
-                      "rot": {"base": base, "dims": rot_dim}}}
+                      "rot": {"base": base, "dims": rot_dims or rot_dim}}}
 
 
 def rec(width, blocks, taps):
@@ -77,6 +77,12 @@ MECHANISMS = {
     "dense_ff": config(61, 32, [layer(attn(2, 8, 8, 12, 16, 2.0), dense(40))], residual_mult=0.5),
     "experts": config(61, 32, [layer(attn(2, 8, 8, 12, 16, 2.0), moe(20, 4, 2, 1))], residual_mult=0.5),
     "loop": config(61, 32, [layer(rec(40, 2, 3), None), layer(attn(2, 8, 8, 12, 16, 2.0), None)], loop=(0, 2, 3)),
+    # of the 8 rotated values only the first 4 turn; a convolution of one tap (nothing is carried but S)
+    "partial_rotation": config(61, 32, [layer(attn(2, 8, 8, 12, 16, 2.0, rot_dims=4), None)]),
+    "one_tap": config(61, 32, [layer(rec(40, 2, 1), dense(24))]),
+    # sizes that are multiples of nothing: every product falls to the CUDA-core kernels, rows of 20 values
+    "odd_sizes": config(53, 44, [layer(attn(3, 10, 6, 14, 14, 1.5), moe(18, 3, 2, 1)), layer(rec(20, 5, 2), dense(30))],
+                        residual_mult=0.6, logit_scale=1.3),
 }
 
 

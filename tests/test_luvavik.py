@@ -455,14 +455,14 @@ def test_latent_attention_kernels_agree(dtype, heads, D, rank, page):
         got = ops.latent_attention(q, cache, bt, step, heads, rank, page, None, 1.0)
         torch.testing.assert_close(got.float(), want.float(), **tol)
     if dtype == torch.bfloat16 and D % 8 == 0 and rank % 8 == 0:
-        # a portion of 150 tokens that follows 100 cached ones, on the tensor cores
-        kv = 250
+        # a portion of 600 tokens that follows 100 cached ones, on the tensor cores (two blocks of queries)
+        n_q, kv = 600, 700
         pages = torch.tensor(perm[:-(-kv // page)], dtype=torch.int32, device=DEV).reshape(1, -1).contiguous()
-        qp = (torch.randn(150, heads * D, generator=gen) * (3.0 / D ** 0.5)).to(dtype).to(DEV)
+        qp = (torch.randn(n_q, heads * D, generator=gen) * (3.0 / D ** 0.5)).to(dtype).to(DEV)
         tr = ops.attention_tile_rows()
-        tiles = -(-150 // tr)
-        pstep = SimpleNamespace(cu_q=i32([0, 150]), kv_lens=i32([kv]), tile_seq=i32([0] * tiles), tile_q0=i32([t * tr for t in range(tiles)]),
-                                dec_seq=i32([0]), n_dec=0, n_seqs=1, q_lens=[150], ctx_lens=[100], max_kv_len=kv)
+        tiles = -(-n_q // tr)
+        pstep = SimpleNamespace(cu_q=i32([0, n_q]), kv_lens=i32([kv]), tile_seq=i32([0] * tiles), tile_q0=i32([t * tr for t in range(tiles)]),
+                                dec_seq=i32([0]), n_dec=0, n_seqs=1, q_lens=[n_q], ctx_lens=[100], max_kv_len=kv)
         try:
             ops.ATTENTION_BACKEND = "generic"
             want = ops.latent_attention(qp, cache, pages, pstep, heads, rank, page, None, 1.0)

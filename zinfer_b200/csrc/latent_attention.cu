@@ -74,8 +74,9 @@ latent_prepare_kernel(const T* __restrict__ src, int ld, int heads, int dim, int
 
 // A request's cached rows, gathered from its pages for the tensor-core products of a prompt's portion:
 // keys[j, :] = row j (all D columns; rows kv_len .. kv_pad-1 are zero) and values_t[r, j] = row j's
-// column r for r < rank (the latent part, transposed: the second product's weight-side operand), held
-// twice side by side ([rank, 2 kv_pad]) because the softmax weights come as a high and a low part.
+// column r for r < rank (the latent part, transposed: the second product's weight-side operand), every
+// value twice in a row ([rank, 2 kv_pad]: columns 2j and 2j+1 hold key j) because the softmax weights come
+// as a high and a low part side by side; a prefix of 2k columns then serves the first k keys.
 // One block takes 32 keys.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -100,8 +101,8 @@ latent_gather_kernel(T* __restrict__ keys, T* __restrict__ values_t, const T* __
   for (int e = threadIdx.x; e < 32 * rank; e += blockDim.x) {
     const int r = e / 32, kk = e - r * 32, j = j0 + kk;
     if (j < kv_pad) {
-      values_t[(size_t)r * 2 * kv_pad + j] = tile[kk * pitch + r];
-      values_t[(size_t)r * 2 * kv_pad + kv_pad + j] = tile[kk * pitch + r];
+      values_t[(size_t)r * 2 * kv_pad + 2 * j] = tile[kk * pitch + r];
+      values_t[(size_t)r * 2 * kv_pad + 2 * j + 1] = tile[kk * pitch + r];
     }
   }
 }
@@ -109,7 +110,7 @@ latent_gather_kernel(T* __restrict__ keys, T* __restrict__ values_t, const T* __
 // Causal softmax over a portion's scores: row (t, h) of S [rows, kv_pad] (32-bit) belongs to the query at
 // position ctx + t and sees keys 0 .. ctx + t; p = exp(scale * (S - max)) / sum there, 0 beyond (also in
 // the padding columns).  The weights are 32-bit; for the second product each is written as two values of
-// the activations' type, P[row, j] = round(p) and P[row, kv_pad + j] = round(p - P[row, j]), whose sum
+// the activations' type, P[row, 2j] = round(p) and P[row, 2j+1] = round(p - P[row, 2j]), whose sum
 // carries 16 bits of p, so that the product loses nothing a 32-bit weight would have kept.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -137,8 +138,8 @@ causal_softmax_kernel(T* __restrict__ P, const float* __restrict__ S, int heads,
   for (int j = threadIdx.x; j < kv_pad; j += blockDim.x) {
     const float w = j < visible ? expf(scale * (s[j] - m)) * inv : 0.f;
     const T hi = from_f32<T>(w);
-    p[j] = hi;
-    p[kv_pad + j] = from_f32<T>(w - to_f32(hi));
+    p[2 * j] = hi;
+    p[2 * j + 1] = from_f32<T>(w - to_f32(hi));
   }
 }
 

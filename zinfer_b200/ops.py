@@ -399,7 +399,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     M, K = x.shape
     N, K2 = weight.shape
     _need(K == K2, f"linear: x has {K} columns, weight has {K2}")
-    _need(x.stride(1) == 1 and weight.is_contiguous(), "linear: operands must be dense along K")
+    _need(x.stride(1) == 1 and weight.stride(1) == 1, "linear: operands must be dense along K")
     if (GEMM_BACKEND != "simt" and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and M > 0
             and lib().zi_gemm_tcgen05_supported(_ptr(x), _ptr(weight), K, x.stride(0), weight.stride(0))):
         plan = (ctypes.c_int * 3)()
@@ -782,6 +782,7 @@ def latent_prepare(proj: torch.Tensor, heads: int, dim: int, rot_dim: int, rank:
 # A request that brings this many tokens or more in a bfloat16 step has its latent attention on the
 # tensor cores (two products around a causal softmax); fewer go to the exact kernel.
 LATENT_TENSOR_MIN_TOKENS = 32
+LATENT_QUERY_BLOCK = 512      # queries per pair of products of a long portion
 
 
 def latent_attention(q_eff: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, step, heads: int, rank: int,
@@ -867,12 +868,18 @@ def _latent_attention_portion(q: torch.Tensor, out: torch.Tensor, cache: torch.T
     with _prof.region("latent attention: gather rows", lambda: 2 * _nb(keys) + _nb(values_t)):
         _check(lib().zi_latent_gather(_ptr(keys), _ptr(values_t), _ptr(cache), _tag(cache), _ptr(_i32(block_table, "block_table")),
                                       page_size, kv, kv_pad, D, rank, _stream()), "latent_gather")
-    scores = linear(q.view(rows, D), keys, out_dtype=torch.float32, fresh_weight=True)
-    probs = torch.empty((rows, 2 * kv_pad), dtype=q.dtype, device=dev)
-    with _prof.region("latent attention: causal softmax", lambda: _nb(scores, probs)):
-        _check(lib().zi_causal_softmax(_ptr(probs), _ptr(scores), _tag(probs), ctypes.c_longlong(rows), heads, ctx, kv_pad,
-                                       ctypes.c_float(scale), _stream()), "causal_softmax")
-    linear(probs, values_t, out=out.view(rows, rank), fresh_weight=True)
+    # in blocks of queries: a block multiplies with the keys up to its own last position only, so about
+    # five eighths of the rectangle of a whole prompt are computed instead of all of it
+    for q0 in range(0, n, LATENT_QUERY_BLOCK):
+        q1 = min(n, q0 + LATENT_QUERY_BLOCK)
+        rows_b = (q1 - q0) * heads
+        kvb = min(kv_pad, -(-(ctx + q1) // 8) * 8)
+        scores = linear(q[q0:q1].view(rows_b, D), keys[:kvb], out_dtype=torch.float32, fresh_weight=True)
+        probs = torch.empty((rows_b, 2 * kvb), dtype=q.dtype, device=dev)
+        with _prof.region("latent attention: causal softmax", lambda: _nb(scores, probs)):
+            _check(lib().zi_causal_softmax(_ptr(probs), _ptr(scores), _tag(probs), ctypes.c_longlong(rows_b), heads, ctx + q0,
+                                           kvb, ctypes.c_float(scale), _stream()), "causal_softmax")
+        linear(probs, values_t[:, :2 * kvb], out=out[q0:q1].view(rows_b, rank), fresh_weight=True)
 
 
 # ----------------------------------------------------------------------- attention
