@@ -72,11 +72,13 @@ struct GemmArgs {
   long long out_group_stride;
 };
 
-constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2;
+constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2, EPI_GEGLU = 3;   // GEGLU: the gate through gelu-tanh
 
-// act(gate) * up: silu, or the tanh form of gelu (ZI_ACT_GELU_TANH); the choice is uniform over a launch
-__device__ __forceinline__ float gated_mul(int act, float g, float u) {
-  return (act == ZI_ACT_GELU_TANH ? gelu_tanh_f32(g) : g / (1.0f + expf(-g))) * u;
+// act(gate) * up: silu, or the tanh form of gelu.  The choice is made when the kernel is compiled: a test per
+// element, even one that always goes the same way, slowed this epilogue measurably.
+template <int EPI>
+__device__ __forceinline__ float gated_mul(float g, float u) {
+  return (EPI == EPI_GEGLU ? gelu_tanh_f32(g) : g / (1.0f + expf(-g))) * u;
 }
 
 // One thread's row of an accumulator (TMEM lane `lane_base`, BN columns) to memory: row `a` of the A
@@ -86,7 +88,7 @@ template <typename TO, int EPI>
 __device__ __forceinline__ void drain_accumulator(const GemmArgs& g, TO* __restrict__ out, float* __restrict__ partial,
                                                   int split, int a, bool a_ok, int b_tile, uint32_t lane_base) {
   const int BN = g.BN;
-  constexpr bool SWIGLU = EPI == EPI_SWIGLU;
+  constexpr bool SWIGLU = EPI == EPI_SWIGLU || EPI == EPI_GEGLU;
   if (SWIGLU) {
     // Tokens on the lanes; of every 128 columns the first 64 are gate and the next 64 up.
     for (int c0 = 0; c0 < BN; c0 += 128) {
@@ -102,16 +104,16 @@ __device__ __forceinline__ void drain_accumulator(const GemmArgs& g, TO* __restr
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             uint4 w;
-            w.x = pack2(gated_mul(g.act, gv[j], uv[j]), gated_mul(g.act, gv[j + 1], uv[j + 1]));
-            w.y = pack2(gated_mul(g.act, gv[j + 2], uv[j + 2]), gated_mul(g.act, gv[j + 3], uv[j + 3]));
-            w.z = pack2(gated_mul(g.act, gv[j + 4], uv[j + 4]), gated_mul(g.act, gv[j + 5], uv[j + 5]));
-            w.w = pack2(gated_mul(g.act, gv[j + 6], uv[j + 6]), gated_mul(g.act, gv[j + 7], uv[j + 7]));
+            w.x = pack2(gated_mul<EPI>(gv[j], uv[j]), gated_mul<EPI>(gv[j + 1], uv[j + 1]));
+            w.y = pack2(gated_mul<EPI>(gv[j + 2], uv[j + 2]), gated_mul<EPI>(gv[j + 3], uv[j + 3]));
+            w.z = pack2(gated_mul<EPI>(gv[j + 4], uv[j + 4]), gated_mul<EPI>(gv[j + 5], uv[j + 5]));
+            w.w = pack2(gated_mul<EPI>(gv[j + 6], uv[j + 6]), gated_mul<EPI>(gv[j + 7], uv[j + 7]));
             *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(o) + j) = w;
           }
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (f0 + j < g.b_rows / 2) o[j] = from_f32<TO>(gated_mul(g.act, gv[j], uv[j]));
+            if (f0 + j < g.b_rows / 2) o[j] = from_f32<TO>(gated_mul<EPI>(gv[j], uv[j]));
         }
       }
     }
@@ -825,6 +827,7 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
                 int head_groups = 0, int a_group_cols = 0, long long out_group_stride = 0) {
   const int swap = plan[0], BN = plan[1], splits = plan[2];
   const int swiglu = epi == EPI_SWIGLU;
+  const bool geglu = swiglu && act == ZI_ACT_GELU_TANH;
   GemmArgs g;
   g.tile_group = tile_group;
   g.group_rows = N;
@@ -873,7 +876,7 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
 
   if (tile_group && (swap || g.splits != 1 || epi != EPI_PLAIN))
     return zi_refuse("%s: the grouped product runs unsplit with the tokens on the lanes", what);
-  if (!tile_group && !head_groups && use_pair_kernel(plan, M)) {
+  if (!tile_group && !head_groups && !geglu && use_pair_kernel(plan, M)) {
     ZI_DISPATCH_DTYPE(out_dtype, TO, { return launch_pair<TO>(out, map_a, map_b, g, M, N, K, status, swiglu, what, stream); });
   }
   if (epi == EPI_ARGMAX) {
@@ -882,7 +885,8 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
     return launch_single<float, EPI_ARGMAX>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream);
   }
   ZI_DISPATCH_DTYPE(out_dtype, TO, {
-    int rc = swiglu ? launch_single<TO, EPI_SWIGLU>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
+    int rc = geglu ? launch_single<TO, EPI_GEGLU>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
+           : swiglu ? launch_single<TO, EPI_SWIGLU>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
                     : launch_single<TO, EPI_PLAIN>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream);
     if (rc) return rc;
     if (partial && !defer_reduce) {
