@@ -72,7 +72,7 @@ struct GemmArgs {
   long long out_group_stride;
 };
 
-constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2, EPI_GEGLU = 3;   // GEGLU: the gate through gelu-tanh
+constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2, EPI_GEGLU = 3, EPI_RELU2 = 4;   // GEGLU: the gate through gelu-tanh; RELU2: plain with the square of relu
 
 // act(gate) * up: silu, or the tanh form of gelu.  The choice is made when the kernel is compiled: a test per
 // element, even one that always goes the same way, slowed this epilogue measurably.
@@ -130,7 +130,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmArgs& g, TO* __restr
     }
     const int ncol = min(32, BN - c0);
     const int b0 = b_tile * BN + c0;
-    if (EPI == EPI_PLAIN && g.relu2) {
+    if (EPI == EPI_RELU2) {      // chosen when the kernel is compiled: the plain epilogue carries nothing for it
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const float r = fmaxf(v[j], 0.f);
@@ -885,7 +885,8 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
     return launch_single<float, EPI_ARGMAX>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream);
   }
   ZI_DISPATCH_DTYPE(out_dtype, TO, {
-    int rc = geglu ? launch_single<TO, EPI_GEGLU>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
+    int rc = relu2 ? launch_single<TO, EPI_RELU2>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
+           : geglu ? launch_single<TO, EPI_GEGLU>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
            : swiglu ? launch_single<TO, EPI_SWIGLU>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
                     : launch_single<TO, EPI_PLAIN>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream);
     if (rc) return rc;
