@@ -124,7 +124,9 @@ template <> struct Vec4<__nv_bfloat16> {
 };
 
 // PART: the update comes as split-K partial sums (`dpart`), else whole (`delta`) or not at all.
-template <typename TD, typename TO, int VPT, bool PART>
+// EXTRA: the update is multiplied by dscale and a bias vector may be added (compiled apart: the plain
+// add keeps its code).
+template <typename TD, typename TO, int VPT, bool PART, bool EXTRA>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta,
                                        const float* __restrict__ dpart, int splits, size_t zstride,
                                        const float* __restrict__ w, float eps, TO* __restrict__ out,
@@ -181,17 +183,28 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
           const float4 p = Vec4<float>::load(base + (size_t)z * zstride);
           d.x += p.x; d.y += p.y; d.z += p.z; d.w += p.w;
         }
-        a.x = fmaf(dscale, d.x, a.x); a.y = fmaf(dscale, d.y, a.y); a.z = fmaf(dscale, d.z, a.z); a.w = fmaf(dscale, d.w, a.w);
+        if (EXTRA) {
+          a.x = fmaf(dscale, d.x, a.x); a.y = fmaf(dscale, d.y, a.y); a.z = fmaf(dscale, d.z, a.z); a.w = fmaf(dscale, d.w, a.w);
+        } else {
+          a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+        }
+        if (!EXTRA && !rows) Vec4<float>::store(hr + 4 * idx, a);   // picked rows leave h as it is (a row may be picked twice)
       } else if (delta) {
         const float4 d = Vec4<TD>::load(delta + (size_t)row * H + 4 * idx);
-        a.x = fmaf(dscale, d.x, a.x); a.y = fmaf(dscale, d.y, a.y); a.z = fmaf(dscale, d.z, a.z); a.w = fmaf(dscale, d.w, a.w);
+        if (EXTRA) {
+          a.x = fmaf(dscale, d.x, a.x); a.y = fmaf(dscale, d.y, a.y); a.z = fmaf(dscale, d.z, a.z); a.w = fmaf(dscale, d.w, a.w);
+        } else {
+          a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+        }
+        if (!EXTRA && !rows) Vec4<float>::store(hr + 4 * idx, a);
       }
-      if (bias) {
-        const float4 b = Vec4<float>::load(bias + 4 * idx);
-        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+      if (EXTRA) {
+        if (bias) {
+          const float4 b = Vec4<float>::load(bias + 4 * idx);
+          a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        if (!rows && (PART || delta || bias)) Vec4<float>::store(hr + 4 * idx, a);
       }
-      // picked rows leave h as it is (a row may be picked twice)
-      if (!rows && (PART || delta || bias)) Vec4<float>::store(hr + 4 * idx, a);
       v[i] = a;
       ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
     }
@@ -230,6 +243,7 @@ static int launch_add_rmsnorm(float* h, const void* delta, const float* dpart, i
                        ((uintptr_t)out % 16 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)dpart % 16 == 0) &&
                        zstride % 4 == 0;
   const int nvec = H / 4;
+  const bool extra = dscale != 1.0f || bias != nullptr;
   // few rows (decode): one vector per thread, so that a row's loads are all in flight at once
   // many rows (a prompt): blocks of 512 with two vectors a thread keep the most bytes in flight per SM (measured:
   // 8,192 rows of 4,096 in 70 us against 76 with 256 threads and 97 with 128)
@@ -237,9 +251,9 @@ static int launch_add_rmsnorm(float* h, const void* delta, const float* dpart, i
   if (aligned && nvec <= threads * 8) {
     const int vpt = (nvec + threads - 1) / threads;
     // as many blocks as are resident at once (asked once per kernel and block size), or one per row if those are fewer
-#define ZI_LAUNCH_VPT(V, P)                                                                                        \
+#define ZI_LAUNCH_VPT(V, P, X)                                                                                     \
   do {                                                                                                             \
-    auto kern = add_rmsnorm_vec_kernel<TD, TO, V, P>;                                                              \
+    auto kern = add_rmsnorm_vec_kernel<TD, TO, V, P, X>;                                                           \
     static int per_sm[3] = {0, 0, 0};                                                                              \
     int& slot = per_sm[threads == 256 ? 0 : threads == 512 ? 1 : 2];                                               \
     if (slot == 0 && (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&slot, kern, threads, 0) != cudaSuccess || slot < 1)) \
@@ -248,10 +262,15 @@ static int launch_add_rmsnorm(float* h, const void* delta, const float* dpart, i
     zi_launch(kern, dim3(n_rows < resident ? n_rows : resident), dim3(threads), 0, stream, h, (const TD*)delta, dpart, \
               splits, zstride, w, eps, (TO*)out, rows, H, n_rows, dscale, bias);                                   \
   } while (0)
-#define ZI_LAUNCH_PART(V)            \
-  do {                               \
-    if (dpart) ZI_LAUNCH_VPT(V, true); \
-    else ZI_LAUNCH_VPT(V, false);    \
+#define ZI_LAUNCH_PART(V)                                \
+  do {                                                   \
+    if (extra) {                                         \
+      if (dpart) ZI_LAUNCH_VPT(V, true, true);           \
+      else ZI_LAUNCH_VPT(V, false, true);                \
+    } else {                                             \
+      if (dpart) ZI_LAUNCH_VPT(V, true, false);          \
+      else ZI_LAUNCH_VPT(V, false, false);               \
+    }                                                    \
   } while (0)
     if (vpt <= 1) ZI_LAUNCH_PART(1);
     else if (vpt <= 2) ZI_LAUNCH_PART(2);

@@ -56,20 +56,25 @@ struct GemmArgs {
   int* cand_idx;
   int cand_units;
   int weights_once;          // few tokens: the weight tiles are loaded with the L2 policy "evict first"
+  static constexpr bool ext = false;
+};
+
+// The arguments of the forms with groups.  They are a type of their own, and the kernel is compiled apart for
+// them, so that the plain product's arguments and code stay what they were.
+struct GemmExtArgs : GemmArgs {
   // Grouped form (tokens on the lanes): the weight is a stack of groups of `group_rows` rows each (the
   // experts of a mixture), and the tile of token rows a_tile multiplies with group tile_group[a_tile].
   const int* tile_group;
   int group_rows;
-  int relu2;                 // plain epilogue: the square of relu before the store
   int late_weights;          // the weight-side operand is written by a kernel of this step: nothing is
                              // requested before the wait for the kernels before this one
-  int act;                   // gated epilogue: ZI_ACT_SILU or ZI_ACT_GELU_TANH
   // Strided groups (one product per head in one launch; tokens on the lanes): the a_tiles are `group_tiles`
   // tiles of token rows for each group in turn; group n reads its activations a_group_cols columns further
   // right in the same rows, its weights group_rows rows further down the stack, and writes its results
   // out_group_stride elements further on.  a_rows then counts the rows of one group.
   int group_tiles, a_group_cols;
   long long out_group_stride;
+  static constexpr bool ext = true;
 };
 
 constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2, EPI_GEGLU = 3, EPI_RELU2 = 4;   // GEGLU: the gate through gelu-tanh; RELU2: plain with the square of relu
@@ -206,10 +211,13 @@ __device__ __forceinline__ void drain_accumulator(const GemmArgs& g, TO* __restr
 // tensor memory let the epilogue of one tile run under the MMAs of the next.
 // EPI_SWIGLU: the epilogue writes silu(gate) * up (tokens on the lanes only).  EPI_ARGMAX: it also
 // leaves each token's largest result per 32 weight rows (weight rows on the lanes only).
-template <typename TO, int EPI>
+// ARGS = GemmExtArgs: the forms with groups (a group per tile, groups side by side in the rows) and with a
+// weight-side operand written earlier in the step.
+template <typename TO, int EPI, typename ARGS = GemmArgs>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    TO* __restrict__ out, float* __restrict__ partial, const GemmArgs g, int* __restrict__ status) {
+                    TO* __restrict__ out, float* __restrict__ partial, const ARGS g, int* __restrict__ status) {
+  constexpr bool EXT = ARGS::ext;
   pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -271,15 +279,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       decode(blockIdx.x, a_tile, b_tile, split, kb0, n_kb);
       // grouped: which group a tile takes is written by a kernel before this one, so nothing is
       // requested before the wait for it
-      const int pre = (g.tile_group || g.late_weights) ? 0 : min(stages, n_kb);
+      int pre = min(stages, n_kb);
+      if constexpr (EXT) {
+        if (g.tile_group || g.late_weights) pre = 0;
+      }
       // which: 1 = the weight's tile of k-block i into stage s, 0 = the activations'
       const uint64_t once = l2_policy_evict_first();
-      int group_tile = -1, group_row0 = 0;     // the tile whose group's first weight row is known
+      [[maybe_unused]] int group_tile = -1, group_row0 = 0;     // the tile whose group's first weight row is known
       auto issue = [&](int which, int s, int i) {
         uint8_t* dst = smem + (size_t)s * stage_bytes;
         const bool use_a = (which != 0) == (g.a_is_weight != 0);
         if (which != 0 && g.weights_once) {
           tma_load_2d_hint(dst, &map_a, &full[s], (kb0 + i) * BLOCK_K, a_tile * TILE_A, once);
+        } else if constexpr (!EXT) {
+          tma_load_2d(use_a ? dst : dst + A_TILE_BYTES, use_a ? &map_a : &map_b, &full[s], (kb0 + i) * BLOCK_K,
+                      use_a ? a_tile * TILE_A : b_tile * BN);
         } else {
           int b_row = b_tile * BN, a_row = a_tile * TILE_A, a_col = (kb0 + i) * BLOCK_K;
           if (g.tile_group && !use_a) {
@@ -368,10 +382,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tcgen05_fence_after();
       int a = a_tile * TILE_A + quarter * 32 + lane;
       TO* out_tile = out;
-      if (g.group_tiles) {      // the row within its group, and the group's place in the output
-        const int grp = a_tile / g.group_tiles;
-        a -= grp * g.group_tiles * TILE_A;
-        out_tile = out + (long long)grp * g.out_group_stride;
+      if constexpr (EXT) {
+        if (g.group_tiles) {      // the row within its group, and the group's place in the output
+          const int grp = a_tile / g.group_tiles;
+          a -= grp * g.group_tiles * TILE_A;
+          out_tile = out + (long long)grp * g.out_group_stride;
+        }
       }
       const uint32_t lane_base = tmem_base + acc * (uint32_t)g.acc_cols + ((uint32_t)(quarter * 32) << 16);
       const bool a_ok = a < g.a_rows;
@@ -794,10 +810,10 @@ int launch_pair(void* out, const CUtensorMap& map_a, const CUtensorMap& map_b, G
 
 // One launch of the single-CTA kernel: as many CTAs as fit on the GPU at once, by shared memory and
 // by tensor memory (512 columns per SM), or one per tile if those are fewer.
-template <typename TO, int EPI>
-int launch_single(void* out, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& g, float* partial,
+template <typename TO, int EPI, typename ARGS = GemmArgs>
+int launch_single(void* out, const CUtensorMap& map_a, const CUtensorMap& map_b, const ARGS& g, float* partial,
                   int* status, int sm_count, size_t smem, int total_tiles, const char* what, cudaStream_t stream) {
-  auto kern = gemm_tcgen05_kernel<TO, EPI>;
+  auto kern = gemm_tcgen05_kernel<TO, EPI, ARGS>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return zi_refuse("%s: cannot get %zu bytes of shared memory", what, smem);
   int per_sm = (int)((227 * 1024) / (smem + 1024));
@@ -828,11 +844,9 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
   const int swap = plan[0], BN = plan[1], splits = plan[2];
   const int swiglu = epi == EPI_SWIGLU;
   const bool geglu = swiglu && act == ZI_ACT_GELU_TANH;
-  GemmArgs g;
+  GemmExtArgs g;
   g.tile_group = tile_group;
   g.group_rows = N;
-  g.relu2 = relu2;
-  g.act = act;
   g.group_tiles = 0;
   g.a_group_cols = a_group_cols;
   g.out_group_stride = out_group_stride;
@@ -882,13 +896,16 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
   if (epi == EPI_ARGMAX) {
     if (out_dtype != ZI_F32 || !swap || g.splits != 1 || !cand_val || !cand_idx)
       return zi_refuse("%s: the argmax epilogue takes 32-bit results of an unsplit product of at most 128 tokens", what);
-    return launch_single<float, EPI_ARGMAX>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream);
+    return launch_single<float, EPI_ARGMAX, GemmArgs>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream);
   }
   ZI_DISPATCH_DTYPE(out_dtype, TO, {
-    int rc = relu2 ? launch_single<TO, EPI_RELU2>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
-           : geglu ? launch_single<TO, EPI_GEGLU>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
-           : swiglu ? launch_single<TO, EPI_SWIGLU>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
-                    : launch_single<TO, EPI_PLAIN>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream);
+    const bool ext = g.tile_group || g.late_weights || g.group_tiles;
+    const GemmArgs& plain = g;      // the plain product takes its own arguments only
+    int rc = relu2 ? launch_single<TO, EPI_RELU2, GemmExtArgs>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
+           : (ext && !swiglu) ? launch_single<TO, EPI_PLAIN, GemmExtArgs>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
+           : geglu ? launch_single<TO, EPI_GEGLU, GemmArgs>(out, map_a, map_b, plain, partial, status, sm_count, smem, total_tiles, what, stream)
+           : swiglu ? launch_single<TO, EPI_SWIGLU, GemmArgs>(out, map_a, map_b, plain, partial, status, sm_count, smem, total_tiles, what, stream)
+                    : launch_single<TO, EPI_PLAIN, GemmArgs>(out, map_a, map_b, plain, partial, status, sm_count, smem, total_tiles, what, stream);
     if (rc) return rc;
     if (partial && !defer_reduce) {
       const size_t total = (size_t)M * N;
