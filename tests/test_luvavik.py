@@ -285,6 +285,32 @@ def test_greedy_generation_through_the_engine(tmp_path, models):
 
 
 @gpu
+def test_command_line_generates(tmp_path):
+    """bin/zinfer: a model folder of random weights made from a Luvavik config.json, greedy tokens in float32 as the
+    plain model gives them, and sampled tokens with the reference's options (the sampling kernel on this vocabulary)."""
+    import os
+    import subprocess
+    import sys
+
+    cfg = U.CONFIGS["flat"]
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(cfg))
+    d = str(tmp_path / "random")
+    tool = os.path.join(ru.REPO, "bin", "zinfer")
+    r = subprocess.run([sys.executable, tool, "random-model", d, str(cfg_path), "7"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    pcfg, w = P.load_model(d)
+    r = subprocess.run([sys.executable, tool, "generate-token-ids", d, "5,17,3,60,2", "6", "--dtype", "float32"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    want = [5, 17, 3, 60, 2] + P.greedy(pcfg, w, [5, 17, 3, 60, 2], 6)
+    assert "tokens: [" + ", ".join(map(str, want)) + "]" in r.stdout
+    r = subprocess.run([sys.executable, tool, "generate-token-ids", d, "5,17,3,60,2", "6", "--temperature", "0.8", "--top-k", "10",
+                        "--seed", "3"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "tokens: [5, 17, 3, 60, 2, " in r.stdout, r.stderr[-2000:]
+
+
+@gpu
 def test_replay_program(tmp_path, models):
     """bin/trace_run as a user runs it: the model class comes from config.json, four state slots."""
     cfg, weights, reqs, plain = models["flat"]
