@@ -90,11 +90,11 @@ def swiglu(gate_up, out=None, out_dtype=None, interleave=0, activation="silu"):
     return (g / (1.0 + torch.exp(-g)) * u).to(out_dtype or gate_up.dtype)
 
 
-def rope_table(n_pos, head_dim, theta, device):
+def rope_table(n_pos, head_dim, theta, device, factor=1.0):
     half = head_dim // 2
     exponent = (np.arange(half, dtype=np.float32) * np.float32(2)) / np.float32(head_dim)
     p = np.power(np.float64(np.float32(theta)), exponent.astype(np.float64)).astype(np.float32)
-    inv = (np.float32(1) / p).astype(np.float32)
+    inv = ((np.float32(1) / p).astype(np.float32) / np.float32(factor)).astype(np.float32)
     ang = (np.arange(n_pos, dtype=np.float32)[:, None] * inv[None, :]).astype(np.float32)
     cos = torch.from_numpy(np.cos(ang.astype(np.float64)).astype(np.float32)).to(device)
     sin = torch.from_numpy(np.sin(ang.astype(np.float64)).astype(np.float32)).to(device)

@@ -1,6 +1,7 @@
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, default_schedule
 from .qwen3 import ConfigError, Qwen3Config, qwen3_model_spec
 from .luvavik import LuvavikConfig, luvavik_model_spec
+from .rogosun import RogosunConfig, rogosun_model_spec
 from .registry import (Family, UnknownArchitecture, family_for, load_config, register_family, registered,
                        unregister_family)
 
@@ -10,8 +11,11 @@ register_family(Family(name="Qwen3ForCausalLM", model_type="qwen3", config_class
 register_family(Family(name="Luvavik", model_type="luvavik", config_class=LuvavikConfig,
                        model_spec=luvavik_model_spec), replace=True)
 
+register_family(Family(name="Rogosun", model_type="rogosun", config_class=RogosunConfig,
+                       model_spec=rogosun_model_spec), replace=True)
+
 __all__ = [
     "ConfigError", "Family", "LayerSpec", "LuvavikConfig", "ModelSpec", "PartSpec", "Qwen3Config", "luvavik_model_spec", "ScheduleEntry",
     "UnknownArchitecture", "default_schedule", "family_for", "load_config", "qwen3_model_spec",
-    "register_family", "registered", "unregister_family",
+    "register_family", "registered", "RogosunConfig", "rogosun_model_spec", "unregister_family",
 ]

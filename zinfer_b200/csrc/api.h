@@ -111,6 +111,41 @@ int zi_paged_attention_v(void* out, int out_stride, const void* q, int q_stride,
                          const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
                          int d, int dv, int v_row, int page_size, int window, float scale, int skip_from,
                          int skip_single, cudaStream_t stream);
+// The same with a sink: `sink` keys of score 0 without a value, counted in the softmax's denominator only.
+int zi_paged_attention_sink(void* out, int out_stride, const void* q, int q_stride, int dtype, const void* kcache,
+                            const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
+                            const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
+                            int d, int dv, int v_row, int page_size, int window, float scale, int skip_from,
+                            int skip_single, float sink, cudaStream_t stream);
+// q/k norm, rotation of the first rot_dims dimensions of a head, page write; values of their own or the keys as projected.
+int zi_qk_prepare(const void* src, int dtype, int T, int src_stride, void* q_out, int q_stride, int nq, int nkv, int d,
+                  int rot_dims, const float* qw, const float* kw, float eps, const float* cos_t, const float* sin_t,
+                  int n_table_pos, const int* positions, void* kcache, void* vcache, const int* slots, int page_size,
+                  int v_from_k, int write_kv, cudaStream_t stream);
+int zi_rope_table_scaled(float* cos_t, float* sin_t, int n_pos, int d, float theta, float factor, cudaStream_t stream);
+// h += norm(sa * a + sb * b) * w (the norm of a sublayer's output), x_out = h in the activations' type.
+int zi_norm_residual(float* h, const void* a, int a_dtype, float sa, const void* b, int b_dtype, float sb, const float* w,
+                     float eps, void* x_out, int out_dtype, int T, int H, cudaStream_t stream);
+int zi_cast_rows(void* out, int out_dtype, const float* h, long long n, cudaStream_t stream);
+int zi_relu2(void* x, int dtype, long long n, cudaStream_t stream);
+// Mixers with a matrix-valued state per head (linear attention with decays, with or without the delta rule).
+int zi_short_conv(float* y, int ldy, const void* x, int ldx, int dtype, const float* kern, const float* tail,
+                  long long slot_stride, int C, int taps, int act, const int* cu_q, const int* state_slots, int n_seqs,
+                  int T, cudaStream_t stream);
+int zi_short_conv_carry(float* tail, long long slot_stride, const void* x, int ldx, int dtype, int C, int taps,
+                        const int* cu_q, const int* state_slots, int n_seqs, cudaStream_t stream);
+int zi_decay(float* z, long long rows, int N, int D, const float* bias, const float* a_log, float inv_tau, int mode,
+             cudaStream_t stream);
+int zi_unit_norm(float* x, int ld, int T, int heads, int d, float eps, float scale, cudaStream_t stream);
+int zi_sigmoid_rows(float* out, int ldo, const void* x, int ldx, int dtype, int rows, int W, cudaStream_t stream);
+int zi_linear_recurrence(float* out, int ldo, const void* q, int ldq, const void* k, int ldk, int qk_dtype, const void* v,
+                         int ldv, int v_dtype, const float* decay, int ldg, const float* beta, int ldb, float q_scale,
+                         float* state, long long slot_stride, int H, int G, int D, int V, int delta, const int* cu_q,
+                         const int* state_slots, int n_seqs, cudaStream_t stream);
+int zi_head_norm_gate(void* out, int out_dtype, int ldo, const float* o, int ldi, const float* w, float eps,
+                      const void* gate, int gate_dtype, int ldgate, int act, int T, int heads, int V, cudaStream_t stream);
+int zi_moe_route_grouped(int* chosen, float* weight, const float* logits, int T, int NR, int top, int renormalize,
+                         int score_kind, int groups, int keep, float wscale, cudaStream_t stream);
 // Latent attention: the cached row [normed latent | rotated key part] and the rotated query part of a token.
 int zi_latent_prepare(const void* src, int ld, int dtype, int T, int heads, int dim, int rd, int rank, int rot_dims,
                       const float* cw, float eps, const float* cos_t, const float* sin_t, int n_table_pos,

@@ -25,7 +25,7 @@ paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict_
                        const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_q,
                        const int* __restrict__ kv_lens, const int* __restrict__ tile_seq,
                        const int* __restrict__ tile_q0, int nq, int nkv, int d, int page_size, int window,
-                       float scale, int dv, int v_row, int skip_from, int skip_single) {
+                       float scale, int dv, int v_row, int skip_from, int skip_single, float sink) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float smem[];
@@ -124,7 +124,8 @@ paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict_
   for (int i = 0; i < ROWS_PER_WARP; ++i) {
     const int r = warp * ROWS_PER_WARP + i;
     if (r >= nqv) continue;
-    const float inv = 1.0f / l[i];
+    // a sink: `sink` keys whose score is 0 and which have no value, counted in the denominator only
+    const float inv = 1.0f / (sink > 0.f ? l[i] + sink * expf(-m[i]) : l[i]);
     T* o = out + (size_t)(tok0 + q0 + r) * out_stride + (size_t)h * dv;
 #pragma unroll
     for (int j = 0; j < MAXJ; ++j) {
@@ -151,7 +152,18 @@ extern "C" int zi_paged_attention_v(void* out, int out_stride, const void* q, in
                                     const int* cu_q, const int* kv_lens, const int* tile_seq, const int* tile_q0,
                                     int n_tiles, int nq, int nkv, int d, int dv, int v_row, int page_size, int window,
                                     float scale, int skip_from, int skip_single, cudaStream_t stream) {
+  return zi_paged_attention_sink(out, out_stride, q, q_stride, dtype, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
+                                 tile_seq, tile_q0, n_tiles, nq, nkv, d, dv, v_row, page_size, window, scale, skip_from,
+                                 skip_single, 0.f, stream);
+}
+
+extern "C" int zi_paged_attention_sink(void* out, int out_stride, const void* q, int q_stride, int dtype,
+                                       const void* kcache, const void* vcache, const int* block_tables, int bt_stride,
+                                       const int* cu_q, const int* kv_lens, const int* tile_seq, const int* tile_q0,
+                                       int n_tiles, int nq, int nkv, int d, int dv, int v_row, int page_size, int window,
+                                       float scale, int skip_from, int skip_single, float sink, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (!(sink >= 0.f)) return zi_refuse("paged_attention: the sink's weight must not be negative");
   constexpr int WIDE = 20;   // value columns up to 640 (latent caches); 8 serves every ordinary head size
   if (d <= 0 || d > 32 * WIDE) return zi_refuse("paged_attention: head_dim %d is outside 1..%d", d, 32 * WIDE);
   if (dv <= 0 || dv > d || v_row < dv) return zi_refuse("paged_attention: %d value columns of rows of %d, keys of %d", dv, v_row, d);
@@ -168,7 +180,7 @@ extern "C" int zi_paged_attention_v(void* out, int out_stride, const void* q, in
     }                                                                                                              \
     zi_launch(kern, dim3(grid), dim3(THREADS), smem, stream, (TT*)out, out_stride, (const TT*)q, q_stride,         \
               (const TT*)kcache, (const TT*)vcache, block_tables, bt_stride, cu_q, kv_lens, tile_seq, tile_q0, nq, \
-              nkv, d, page_size, window, scale, dv, v_row, skip_from, skip_single);                                \
+              nkv, d, page_size, window, scale, dv, v_row, skip_from, skip_single, sink);                          \
   } while (0)
   ZI_DISPATCH_DTYPE(dtype, TT, {
     if (dv <= 256) ZI_LAUNCH_ATTN(8);

@@ -474,7 +474,7 @@ extern "C" int zi_gated_act(void* out, const void* gu, int dtype, int T, int I, 
 // sin are evaluated in double and rounded once, so the table holds the correctly
 // rounded value of each 32-bit step.
 __global__ void rope_table_kernel(float* __restrict__ cos_t, float* __restrict__ sin_t, int n_pos, int half,
-                                  int d, float theta) {
+                                  int d, float theta, float factor) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -482,18 +482,25 @@ __global__ void rope_table_kernel(float* __restrict__ cos_t, float* __restrict__
   const int pos = (int)(idx / half), i = (int)(idx % half);
   const float exponent = (float)(2 * i) / (float)d;
   const float p = (float)pow((double)theta, (double)exponent);
-  const float inv_freq = 1.0f / p;
+  const float inv_freq = (1.0f / p) / factor;      // linear scaling: every frequency divided by `factor` (1: none)
   const float angle = (float)pos * inv_freq;
   cos_t[idx] = (float)cos((double)angle);
   sin_t[idx] = (float)sin((double)angle);
 }
 
-extern "C" int zi_rope_table(float* cos_t, float* sin_t, int n_pos, int d, float theta, cudaStream_t stream) {
+extern "C" int zi_rope_table_scaled(float* cos_t, float* sin_t, int n_pos, int d, float theta, float factor,
+                                    cudaStream_t stream) {
   if (d <= 0 || d % 2) return zi_refuse("rope_table: head_dim %d is not even", d);
+  if (!(factor > 0.f)) return zi_refuse("rope_table: the scaling factor must be positive");
   const size_t total = (size_t)n_pos * (d / 2);
   if (total == 0) return 0;
-  zi_launch(rope_table_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, cos_t, sin_t, n_pos, d / 2, d, theta);
+  zi_launch(rope_table_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, cos_t, sin_t, n_pos, d / 2, d, theta,
+            factor);
   return zi_check_launch("rope_table");
+}
+
+extern "C" int zi_rope_table(float* cos_t, float* sin_t, int n_pos, int d, float theta, cudaStream_t stream) {
+  return zi_rope_table_scaled(cos_t, sin_t, n_pos, d, theta, 1.0f, stream);
 }
 
 // ------------------------------------------- q/k RMSNorm + rotary + write into pages
@@ -754,6 +761,160 @@ extern "C" int zi_patch_tokens(int* ids, const int* prev, const int* dst, const 
   if (n <= 0) return 0;
   zi_launch(patch_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids, prev, dst, src, n);
   return zi_check_launch("patch_tokens");
+}
+
+// ------------------------------- q/k norm + rotation of part of a head + page write, general form
+// Rows [q heads | k heads | v heads], or [q heads | k heads] with the values taken from the keys AS
+// PROJECTED (before norm and rotation; v_from_k).  The rotation turns the first rot_dims dimensions of a
+// head in pairs (i, i + rot_dims/2) by tables [positions, rot_dims/2]; the rest passes unchanged.  One
+// warp per (token, head); q is rewritten in place.
+template <typename T>
+__global__ void qk_prepare_kernel(const T* src, int src_stride, T* q_out, int q_stride, int nq, int nkv, int d,
+                                  int rot_dims, const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+                                  const float* __restrict__ cos_t, const float* __restrict__ sin_t, int n_table_pos,
+                                  const int* __restrict__ positions, T* __restrict__ kcache, T* __restrict__ vcache,
+                                  const int* __restrict__ slots, int page_size, int v_from_k, int write_kv, int T_) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n_heads = nq + (write_kv ? (v_from_k ? nkv : 2 * nkv) : 0);
+  const int wi = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (wi >= T_ * n_heads) return;
+  const int t = wi / n_heads, head = wi % n_heads;
+  const T* x = src + (size_t)t * src_stride + (size_t)head * d;
+  T* dst;
+  T* vdst = nullptr;
+  if (head < nq) {
+    dst = q_out + (size_t)t * q_stride + (size_t)head * d;
+  } else {
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int kvh = (head - nq) % nkv;
+    const size_t at = (((size_t)(slot / page_size) * nkv + kvh) * page_size + (slot % page_size)) * d;
+    if (head >= nq + nkv) {            // a value head of its own: copy
+      for (int i = lane; i < d; i += 32) vcache[at + i] = x[i];
+      return;
+    }
+    dst = kcache + at;
+    if (v_from_k) vdst = vcache + at;
+  }
+  const float* w = head < nq ? qw : kw;
+  float ss = 0.f;
+  for (int i = lane; i < d; i += 32) {
+    const float v = to_f32(x[i]);
+    ss = fmaf(v, v, ss);
+    if (vdst) vdst[i] = x[i];
+  }
+  float inv = 1.f;
+  if (w) inv = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
+  int pos = positions[t];
+  if (pos >= n_table_pos) pos = n_table_pos - 1;   // the host refuses such positions
+  const int half = rot_dims >> 1;
+  for (int i = lane; i < half; i += 32) {
+    float a = to_f32(x[i]), b = to_f32(x[i + half]);
+    if (w) {
+      a = norm_scale(a, w[i], inv);
+      b = norm_scale(b, w[i + half], inv);
+    }
+    if (cos_t) rotate_pair(a, b, cos_t[(size_t)pos * half + i], sin_t[(size_t)pos * half + i]);
+    dst[i] = from_f32<T>(a);
+    dst[i + half] = from_f32<T>(b);
+  }
+  for (int i = rot_dims + lane; i < d; i += 32) {
+    float a = to_f32(x[i]);
+    if (w) a = norm_scale(a, w[i], inv);
+    dst[i] = from_f32<T>(a);
+  }
+}
+
+extern "C" int zi_qk_prepare(const void* src, int dtype, int T, int src_stride, void* q_out, int q_stride, int nq, int nkv,
+                             int d, int rot_dims, const float* qw, const float* kw, float eps, const float* cos_t,
+                             const float* sin_t, int n_table_pos, const int* positions, void* kcache, void* vcache,
+                             const int* slots, int page_size, int v_from_k, int write_kv, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (d <= 0 || rot_dims < 0 || rot_dims % 2 || rot_dims > d)
+    return zi_refuse("qk_prepare: %d rotated dimensions of a head of %d", rot_dims, d);
+  if ((cos_t == nullptr) != (sin_t == nullptr)) return zi_refuse("qk_prepare: cos and sin tables go together");
+  if (write_kv && (!kcache || !vcache || !slots || page_size <= 0)) return zi_refuse("qk_prepare: writing keys and values needs pages and slots");
+  const int n_heads = nq + (write_kv ? (v_from_k ? nkv : 2 * nkv) : 0);
+  const int warps = 4;
+  const unsigned blocks = (unsigned)(((size_t)T * n_heads + warps - 1) / warps);
+  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(qk_prepare_kernel<TT>, dim3(blocks), dim3(warps * 32), 0, stream, (const TT*)src,
+                                         src_stride, (TT*)q_out, q_stride, nq, nkv, d, cos_t ? rot_dims : 0, qw, kw, eps, cos_t,
+                                         sin_t, n_table_pos, positions, (TT*)kcache, (TT*)vcache, slots, page_size, v_from_k,
+                                         write_kv, T));
+  return zi_check_launch("qk_prepare");
+}
+
+// ------------------------------------------- norm of a sublayer's OUTPUT, then the residual sum
+// h += norm(sa * a + sb * b) * w with norm(y) = y / sqrt(mean(y^2) + eps); x_out = h in the activations'
+// type (what the next sublayer reads).  b may be absent.  One block per row, 32-bit throughout.
+template <typename TA, typename TB, typename TO>
+__global__ void __launch_bounds__(256)
+norm_residual_kernel(float* __restrict__ h, const TA* __restrict__ a, float sa, const TB* __restrict__ b, float sb,
+                     const float* __restrict__ w, float eps, TO* __restrict__ x_out, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const size_t row = (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float y = sa * to_f32(a[row + c]);
+    if (b) y = fmaf(sb, to_f32(b[row + c]), y);
+    ss = fmaf(y, y, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float y = sa * to_f32(a[row + c]);
+    if (b) y = fmaf(sb, to_f32(b[row + c]), y);
+    const float v = h[row + c] + y * inv * w[c];
+    h[row + c] = v;
+    if (x_out) x_out[row + c] = from_f32<TO>(v);
+  }
+}
+
+extern "C" int zi_norm_residual(float* h, const void* a, int a_dtype, float sa, const void* b, int b_dtype, float sb,
+                                const float* w, float eps, void* x_out, int out_dtype, int T, int H, cudaStream_t stream) {
+  if (T <= 0 || H <= 0) return 0;
+  if (!a) return zi_refuse("norm_residual: no update given");
+  ZI_DISPATCH_DTYPE(a_dtype, TA, ZI_DISPATCH_DTYPE(b ? b_dtype : ZI_F32, TB, ZI_DISPATCH_DTYPE(out_dtype, TO,
+      zi_launch(norm_residual_kernel<TA, TB, TO>, dim3(T), dim3(256), 0, stream, h, (const TA*)a, sa, (const TB*)b, sb, w, eps,
+                (TO*)x_out, H))));
+  return zi_check_launch("norm_residual");
+}
+
+// the 32-bit residual stream in the activations' type
+template <typename TO>
+__global__ void cast_rows_kernel(TO* __restrict__ out, const float* __restrict__ h, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = from_f32<TO>(h[i]);
+}
+
+extern "C" int zi_cast_rows(void* out, int out_dtype, const float* h, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  ZI_DISPATCH_DTYPE(out_dtype, TO, zi_launch(cast_rows_kernel<TO>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream,
+                                             (TO*)out, h, (size_t)n));
+  return zi_check_launch("cast_rows");
+}
+
+// x <- relu(x)^2 in place
+template <typename T>
+__global__ void relu2_kernel(T* __restrict__ x, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const float v = fmaxf(to_f32(x[i]), 0.f);
+    x[i] = from_f32<T>(v * v);
+  }
+}
+
+extern "C" int zi_relu2(void* x, int dtype, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(relu2_kernel<TT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (TT*)x, (size_t)n));
+  return zi_check_launch("relu2");
 }
 
 ZI_TRACE_SETTER(elementwise)

@@ -1,0 +1,338 @@
+// Kernels of mixers that keep a matrix-valued state per head instead of keys (linear attention
+// with a decay per key channel, with or without the delta rule), and of the short convolutions and
+// the gated per-head norm around them.
+//
+// The recurrence, per head, with S [D key channels, V value channels] carried per request:
+//     S <- diag(g_t) S                      the decay acts on the rows that belong to key channels
+//     u_t = v_t                             plain form
+//     u_t = beta_t (v_t - S^T k_t)          delta rule
+//     S <- S + k_t u_t^T ;  o_t = S^T (q_scale q_t)
+// Everything here is 32-bit arithmetic.  A request's tokens of this step are rows cu_q[s] ..
+// cu_q[s+1]-1 of the flat batch and continue the request from slot state_slots[s].  Each column of S
+// is visited by one group of threads, token after token, in an order that depends on D alone, so a
+// result depends neither on how the request was cut into steps nor on the batch.
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float softplus_f32(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float sigmoid_f32(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float log_sigmoid_f32(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+__device__ __forceinline__ int seq_of_token(const int* __restrict__ cu_q, int n_seqs, int t) {
+  int s = 0, hi = n_seqs - 1;          // cu_q[s] <= t < cu_q[s+1]
+  while (s < hi) {
+    const int mid = (s + hi + 1) >> 1;
+    if (cu_q[mid] <= t) s = mid; else hi = mid - 1;
+  }
+  return s;
+}
+
+// ------------------------------------------------------------------ short causal convolution
+// y[t, c] = act(sum_j kern[c, j] * x[t - (taps-1-j), c]), inputs before the step's first token from the
+// carried rows tail[slot][taps-1][C] (oldest first), one thread per (token, channel).
+template <typename T>
+__global__ void short_conv_kernel(float* __restrict__ y, int ldy, const T* __restrict__ x, int ldx,
+                                  const float* __restrict__ kern, const float* __restrict__ tail,
+                                  long long slot_stride, int C, int taps, int act, const int* __restrict__ cu_q,
+                                  const int* __restrict__ state_slots, int n_seqs) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int s = seq_of_token(cu_q, n_seqs, t);
+  const int tok0 = cu_q[s], tl = t - tok0;
+  const float* st = tail + (size_t)state_slots[s] * slot_stride;
+  float acc = 0.f;
+  for (int j = 0; j < taps; ++j) {
+    const int src = tl - (taps - 1 - j);
+    float v;
+    if (src >= 0) v = to_f32(x[(size_t)(tok0 + src) * ldx + c]);
+    else v = st[(size_t)(taps - 1 + src) * C + c];      // src = -1: the newest carried input, row taps-2
+    acc = fmaf(kern[(size_t)c * taps + j], v, acc);
+  }
+  if (act == 1) acc = acc * sigmoid_f32(acc);
+  y[(size_t)t * ldy + c] = acc;
+}
+
+// The carried rows after the step: the last taps-1 inputs of each request, one thread per (request, channel).
+// Row r takes an index above r, so ascending r may overwrite in place.
+template <typename T>
+__global__ void short_conv_carry_kernel(float* __restrict__ tail, long long slot_stride, const T* __restrict__ x, int ldx,
+                                        int C, int taps, const int* __restrict__ cu_q,
+                                        const int* __restrict__ state_slots, int n_seqs) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int s = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C || s >= n_seqs) return;
+  const int tok0 = cu_q[s], qlen = cu_q[s + 1] - tok0;
+  if (qlen <= 0) return;
+  float* st = tail + (size_t)state_slots[s] * slot_stride;
+  for (int r = 0; r < taps - 1; ++r) {
+    const int src = qlen - (taps - 1) + r;
+    st[(size_t)r * C + c] = src >= 0 ? to_f32(x[(size_t)(tok0 + src) * ldx + c]) : st[(size_t)(r + qlen) * C + c];
+  }
+}
+
+// ------------------------------------------------------------------------------- decays
+// mode 0: g = sigmoid(z + bias)^(inv_tau) = exp(log_sigmoid(z + bias) * inv_tau)
+// mode 1: g = exp(-exp(a_log[head]) * softplus(z + bias)), head = column / D
+__global__ void decay_kernel(float* __restrict__ z, size_t total, int N, int D, const float* __restrict__ bias,
+                             const float* __restrict__ a_log, float inv_tau, int mode) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int c = (int)(idx % N);
+  const float x = z[idx] + (bias ? bias[c] : 0.f);
+  z[idx] = mode == 0 ? expf(log_sigmoid_f32(x) * inv_tau) : expf(-expf(a_log[c / D]) * softplus_f32(x));
+}
+
+// x[t, head, :] <- scale * x / sqrt(sum(x^2) + eps), one warp per (token, head), in place
+__global__ void unit_norm_kernel(float* __restrict__ x, int ld, int T, int heads, int d, float eps, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (w >= T * heads) return;
+  float* p = x + (size_t)(w / heads) * ld + (size_t)(w % heads) * d;
+  float ss = 0.f;
+  for (int i = lane; i < d; i += 32) ss = fmaf(p[i], p[i], ss);
+  ss = warp_sum(ss);
+  const float r = scale / sqrtf(ss + eps);
+  for (int i = lane; i < d; i += 32) p[i] *= r;
+}
+
+template <typename T>
+__global__ void sigmoid_rows_kernel(float* __restrict__ out, int ldo, const T* __restrict__ x, int ldx, int rows, int W) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)rows * W) return;
+  const int r = (int)(idx / W), c = (int)(idx % W);
+  out[(size_t)r * ldo + c] = sigmoid_f32(to_f32(x[(size_t)r * ldx + c]));
+}
+
+// --------------------------------------------------------------------------- the recurrence
+// Block: one request, one head, VB = 32 neighbouring value channels.  Thread (p, j) keeps R rows
+// p*R .. p*R+R-1 of column j of S in registers; the sums over a column's rows meet through shared
+// memory in the order p = 0, 1, ...  Tokens are staged TB at a time.
+constexpr int VB = 32, TB = 8;
+
+template <typename TQ, typename TV, int R, bool DELTA>
+__global__ void __launch_bounds__(512)
+linear_recurrence_kernel(float* __restrict__ out, int ldo, const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k,
+                         int ldk, const TV* __restrict__ v, int ldv, const float* __restrict__ decay, int ldg,
+                         const float* __restrict__ beta, int ldb, float q_scale, float* __restrict__ state,
+                         long long slot_stride, int H, int G, int D, int V, int P, const int* __restrict__ cu_q,
+                         const int* __restrict__ state_slots) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  const int DP = P * R;                      // key channels rounded up to whole parts
+  float* qs = sm;                            // [TB][DP]
+  float* ks = qs + TB * DP;                  // [TB][DP]
+  float* gs = ks + TB * DP;                  // [TB][DP]
+  float* vs = gs + TB * DP;                  // [TB][VB]
+  float* kq = vs + TB * VB;                  // [TB]
+  float* bs = kq + TB;                       // [TB]
+  float* red = bs + TB;                      // [2 parities][2 sums][P][VB]
+  const int s = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * VB;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const int p = tid / VB, j = tid % VB, col = j0 + j;
+  const int kvh = h / (H / G);
+  const int tok0 = cu_q[s], qlen = cu_q[s + 1] - tok0;
+  if (qlen <= 0) return;
+  float* S = state + (size_t)state_slots[s] * slot_stride + (size_t)h * D * V;
+  float Sr[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int i = p * R + r;
+    Sr[r] = (i < D && col < V) ? S[(size_t)i * V + col] : 0.f;
+  }
+  for (int t0 = 0; t0 < qlen; t0 += TB) {
+    const int nt = min(TB, qlen - t0);
+    __syncthreads();                         // the staged tokens before are consumed
+    for (int e = tid; e < nt * DP; e += nthreads) {
+      const int tt = e / DP, i = e % DP;
+      const size_t row = (size_t)(tok0 + t0 + tt);
+      const bool in = i < D;
+      qs[e] = in ? to_f32(q[row * ldq + (size_t)kvh * D + i]) * q_scale : 0.f;
+      ks[e] = in ? to_f32(k[row * ldk + (size_t)kvh * D + i]) : 0.f;
+      gs[e] = in ? decay[row * ldg + (size_t)h * D + i] : 0.f;
+    }
+    for (int e = tid; e < nt * VB; e += nthreads) {
+      const int tt = e / VB, c = j0 + e % VB;
+      vs[e] = c < V ? to_f32(v[(size_t)(tok0 + t0 + tt) * ldv + (size_t)h * V + c]) : 0.f;
+    }
+    if (tid < nt) bs[tid] = DELTA ? beta[(size_t)(tok0 + t0 + tid) * ldb + h] : 1.f;
+    __syncthreads();
+    // k . q of each staged token: one warp per token, lanes stride over the channels
+    for (int tt = tid >> 5; tt < nt; tt += nthreads >> 5) {
+      float a = 0.f;
+      for (int i = tid & 31; i < DP; i += 32) a = fmaf(ks[tt * DP + i], qs[tt * DP + i], a);
+      a = warp_sum(a);
+      if ((tid & 31) == 0) kq[tt] = a;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float* qt = qs + tt * DP + p * R;
+      const float* kt = ks + tt * DP + p * R;
+      const float* gt = gs + tt * DP + p * R;
+      float a = 0.f, b = 0.f;               // (g S)^T k and (g S)^T q over this thread's rows
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        Sr[r] *= gt[r];
+        a = fmaf(Sr[r], kt[r], a);
+        b = fmaf(Sr[r], qt[r], b);
+      }
+      if (P > 1) {
+        float* rd = red + (size_t)((t0 + tt) & 1) * 2 * P * VB;
+        rd[p * VB + j] = a;
+        rd[(P + p) * VB + j] = b;
+        __syncthreads();
+        a = 0.f;
+        b = 0.f;
+        for (int pp = 0; pp < P; ++pp) {
+          a += rd[pp * VB + j];
+          b += rd[(P + pp) * VB + j];
+        }
+      }
+      const float vj = vs[tt * VB + j];
+      const float u = DELTA ? bs[tt] * (vj - a) : vj;
+#pragma unroll
+      for (int r = 0; r < R; ++r) Sr[r] = fmaf(kt[r], u, Sr[r]);
+      if (p == 0 && col < V) out[(size_t)(tok0 + t0 + tt) * ldo + (size_t)h * V + col] = fmaf(u, kq[tt], b);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int i = p * R + r;
+    if (i < D && col < V) S[(size_t)i * V + col] = Sr[r];
+  }
+}
+
+// ----------------------------------------------------------------------- gated per-head norm
+// out[t, head, :] = o / sqrt(mean(o^2) + eps) * w * act(gate[t, head, :]); act: 0 silu, 1 sigmoid.
+// One warp per (token, head).
+template <typename TG, typename TO>
+__global__ void head_norm_gate_kernel(TO* __restrict__ out, int ldo, const float* __restrict__ o, int ldi,
+                                      const float* __restrict__ w, float eps, const TG* __restrict__ gate, int ldgate,
+                                      int act, int T, int heads, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int wi = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (wi >= T * heads) return;
+  const int t = wi / heads, h = wi % heads;
+  const float* p = o + (size_t)t * ldi + (size_t)h * V;
+  float ss = 0.f;
+  for (int i = lane; i < V; i += 32) ss = fmaf(p[i], p[i], ss);
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)V + eps);
+  for (int i = lane; i < V; i += 32) {
+    const float g = to_f32(gate[(size_t)t * ldgate + (size_t)h * V + i]);
+    const float a = act == 0 ? g * sigmoid_f32(g) : sigmoid_f32(g);
+    out[(size_t)t * ldo + (size_t)h * V + i] = from_f32<TO>(p[i] * inv * w[i] * a);
+  }
+}
+}  // namespace
+
+extern "C" int zi_short_conv(float* y, int ldy, const void* x, int ldx, int dtype, const float* kern, const float* tail,
+                             long long slot_stride, int C, int taps, int act, const int* cu_q, const int* state_slots,
+                             int n_seqs, int T, cudaStream_t stream) {
+  if (T <= 0 || C <= 0) return 0;
+  if (taps < 1 || taps > 64) return zi_refuse("short_conv: %d taps", taps);
+  dim3 grid((C + 127) / 128, T);
+  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(short_conv_kernel<TT>, dim3(grid), dim3(128), 0, stream, y, ldy, (const TT*)x, ldx,
+                                         kern, tail, slot_stride, C, taps, act, cu_q, state_slots, n_seqs));
+  return zi_check_launch("short_conv");
+}
+
+extern "C" int zi_short_conv_carry(float* tail, long long slot_stride, const void* x, int ldx, int dtype, int C, int taps,
+                                   const int* cu_q, const int* state_slots, int n_seqs, cudaStream_t stream) {
+  if (n_seqs <= 0 || C <= 0 || taps <= 1) return 0;
+  dim3 grid((C + 127) / 128, n_seqs);
+  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(short_conv_carry_kernel<TT>, dim3(grid), dim3(128), 0, stream, tail, slot_stride,
+                                         (const TT*)x, ldx, C, taps, cu_q, state_slots, n_seqs));
+  return zi_check_launch("short_conv_carry");
+}
+
+extern "C" int zi_decay(float* z, long long rows, int N, int D, const float* bias, const float* a_log, float inv_tau,
+                        int mode, cudaStream_t stream) {
+  const size_t total = (size_t)rows * N;
+  if (total == 0) return 0;
+  if (mode != 0 && mode != 1) return zi_refuse("decay: unknown mode %d", mode);
+  if (mode == 1 && (!a_log || D <= 0 || N % D)) return zi_refuse("decay: the per-head form needs a_log and whole heads");
+  zi_launch(decay_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, z, total, N, D, bias, a_log, inv_tau, mode);
+  return zi_check_launch("decay");
+}
+
+extern "C" int zi_unit_norm(float* x, int ld, int T, int heads, int d, float eps, float scale, cudaStream_t stream) {
+  if (T <= 0 || heads <= 0) return 0;
+  const int warps = 4;
+  zi_launch(unit_norm_kernel, dim3((unsigned)((T * heads + warps - 1) / warps)), dim3(warps * 32), 0, stream, x, ld, T, heads, d,
+            eps, scale);
+  return zi_check_launch("unit_norm");
+}
+
+extern "C" int zi_sigmoid_rows(float* out, int ldo, const void* x, int ldx, int dtype, int rows, int W, cudaStream_t stream) {
+  const size_t total = (size_t)rows * W;
+  if (total == 0) return 0;
+  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(sigmoid_rows_kernel<TT>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                                         out, ldo, (const TT*)x, ldx, rows, W));
+  return zi_check_launch("sigmoid_rows");
+}
+
+extern "C" int zi_linear_recurrence(float* out, int ldo, const void* q, int ldq, const void* k, int ldk, int qk_dtype,
+                                    const void* v, int ldv, int v_dtype, const float* decay, int ldg, const float* beta,
+                                    int ldb, float q_scale, float* state, long long slot_stride, int H, int G, int D,
+                                    int V, int delta, const int* cu_q, const int* state_slots, int n_seqs,
+                                    cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (H <= 0 || G <= 0 || H % G) return zi_refuse("linear_recurrence: %d heads do not divide into %d key heads", H, G);
+  if (D <= 0 || D > 512 || V <= 0) return zi_refuse("linear_recurrence: %d key channels (1..512), %d value channels", D, V);
+  if (delta && !beta) return zi_refuse("linear_recurrence: the delta rule needs beta");
+  const int R = D <= 64 ? 16 : 32;
+  const int P = (D + R - 1) / R;
+  const size_t smem = (size_t)(3 * TB * P * R + TB * VB + 2 * TB + 4 * P * VB) * sizeof(float);
+  dim3 grid(n_seqs, H, (V + VB - 1) / VB), block(P * VB);
+#define ZI_LR(TQ, TV, RR, DD)                                                                                          \
+  do {                                                                                                                 \
+    auto kern = linear_recurrence_kernel<TQ, TV, RR, DD>;                                                              \
+    if (smem > 48 * 1024) {                                                                                            \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)           \
+        return zi_refuse("linear_recurrence: cannot get %zu bytes of shared memory", smem);                            \
+    }                                                                                                                  \
+    zi_launch(kern, dim3(grid), dim3(block), smem, stream, out, ldo, (const TQ*)q, ldq, (const TQ*)k, ldk, (const TV*)v, \
+              ldv, decay, ldg, beta, ldb, q_scale, state, slot_stride, H, G, D, V, P, cu_q, state_slots);              \
+  } while (0)
+#define ZI_LR_R(TQ, TV)                                          \
+  do {                                                           \
+    if (R == 16) { if (delta) ZI_LR(TQ, TV, 16, true); else ZI_LR(TQ, TV, 16, false); } \
+    else { if (delta) ZI_LR(TQ, TV, 32, true); else ZI_LR(TQ, TV, 32, false); }         \
+  } while (0)
+  if (qk_dtype == ZI_F32 && v_dtype == ZI_F32) ZI_LR_R(float, float);
+  else if (qk_dtype == ZI_BF16 && v_dtype == ZI_BF16) ZI_LR_R(__nv_bfloat16, __nv_bfloat16);
+  else if (qk_dtype == ZI_F32 && v_dtype == ZI_BF16) ZI_LR_R(float, __nv_bfloat16);
+  else return zi_refuse("linear_recurrence: operand types %d and %d", qk_dtype, v_dtype);
+#undef ZI_LR_R
+#undef ZI_LR
+  return zi_check_launch("linear_recurrence");
+}
+
+extern "C" int zi_head_norm_gate(void* out, int out_dtype, int ldo, const float* o, int ldi, const float* w, float eps,
+                                 const void* gate, int gate_dtype, int ldgate, int act, int T, int heads, int V,
+                                 cudaStream_t stream) {
+  if (T <= 0 || heads <= 0) return 0;
+  if (act != 0 && act != 1) return zi_refuse("head_norm_gate: unknown gate %d", act);
+  const int warps = 4;
+  dim3 grid((unsigned)(((size_t)T * heads + warps - 1) / warps));
+  ZI_DISPATCH_DTYPE(gate_dtype, TG, ZI_DISPATCH_DTYPE(out_dtype, TO,
+      zi_launch(head_norm_gate_kernel<TG, TO>, dim3(grid), dim3(warps * 32), 0, stream, (TO*)out, ldo, o, ldi, w, eps,
+                (const TG*)gate, ldgate, act, T, heads, V)));
+  return zi_check_launch("head_norm_gate");
+}
+
+ZI_TRACE_SETTER(linear_attention)

@@ -80,6 +80,107 @@ __device__ __forceinline__ void route_token(int* __restrict__ chosen, float* __r
   }
 }
 
+// The choice among groups of neighbouring outputs: scores are sigmoid(z) (score_kind 1) or a softmax (0); the
+// outputs form `groups` equal groups, a group's score is the sum of its two largest scores, and only outputs
+// of the `keep` best groups can be chosen; the weight of a chosen output is its score times wscale, divided
+// by the chosen scores' sum first if `renormalize`.  Ties go to the lower index.  score, pick, gsc: NR floats
+// each of shared memory for this warp.
+__device__ __forceinline__ void route_token_grouped(int* __restrict__ chosen, float* __restrict__ weight, const float* z,
+                                                    float* score, float* pick, float* gsc, int t, int NR, int top,
+                                                    int renormalize, int score_kind, int groups, int keep,
+                                                    float wscale, int lane) {
+  if (score_kind == 1) {
+    for (int j = lane; j < NR; j += 32) score[j] = 1.0f / (1.0f + expf(-z[j]));
+  } else {
+    float m = -INFINITY;
+    for (int j = lane; j < NR; j += 32) m = fmaxf(m, z[j]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int j = lane; j < NR; j += 32) {
+      const float e = expf(z[j] - m);
+      score[j] = e;
+      sum += e;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int j = lane; j < NR; j += 32) score[j] *= inv;
+  }
+  __syncwarp();
+  const int per = NR / groups;
+  for (int g = lane; g < groups; g += 32) {      // the two largest scores of the group
+    float a = -INFINITY, b = -INFINITY;
+    for (int i = 0; i < per; ++i) {
+      const float v = score[g * per + i];
+      if (v > a) { b = a; a = v; }
+      else if (v > b) b = v;
+    }
+    gsc[g] = per > 1 ? a + b : a;
+  }
+  __syncwarp();
+  for (int j = lane; j < NR; j += 32) pick[j] = -INFINITY;
+  __syncwarp();
+  for (int n = 0; n < keep; ++n) {               // the best groups, one after the other
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int g = lane; g < groups; g += 32) {
+      const float v = gsc[g];
+      if (v > best) { best = v; arg = g; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    if (arg == 0x7fffffff) break;                // uniform: nothing is left
+    for (int i = lane; i < per; i += 32) pick[arg * per + i] = score[arg * per + i];
+    if (lane == 0) gsc[arg] = -INFINITY;
+    __syncwarp();
+  }
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int j = lane; j < NR; j += 32) {
+      const float v = pick[j];
+      if (v > best) { best = v; arg = j; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    if (arg == 0x7fffffff) arg = 0;
+    const float s = score[arg];
+    total += s;
+    if (lane == 0) {
+      chosen[(size_t)t * top + k] = arg;
+      weight[(size_t)t * top + k] = s * wscale;
+      pick[arg] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (renormalize && lane == 0) {
+    const float r = 1.0f / total;
+    for (int k = 0; k < top; ++k) weight[(size_t)t * top + k] *= r;
+  }
+}
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_grouped_kernel(int* __restrict__ chosen, float* __restrict__ weight, const float* __restrict__ logits, int T,
+                         int NR, int top, int renormalize, int score_kind, int groups, int keep, float wscale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= T) return;
+  float* score = sm + (size_t)warp * 3 * NR;
+  route_token_grouped(chosen, weight, logits + (size_t)t * NR, score, score + NR, score + 2 * NR, t, NR, top, renormalize,
+                      score_kind, groups, keep, wscale, lane);
+}
+
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, const float* __restrict__ logits,
                  const float* __restrict__ correction, int T, int NR, int top, int renormalize) {
@@ -319,6 +420,22 @@ extern "C" int zi_moe_route(int* chosen, float* weight, const float* logits, con
   zi_launch(moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream, chosen,
             weight, logits, correction, T, NR, top, renormalize);
   return zi_check_launch("moe_route");
+}
+
+extern "C" int zi_moe_route_grouped(int* chosen, float* weight, const float* logits, int T, int NR, int top,
+                                    int renormalize, int score_kind, int groups, int keep, float wscale,
+                                    cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (top <= 0 || top > NR) return zi_refuse("moe_route: %d of %d outputs cannot be chosen", top, NR);
+  if (groups <= 0 || NR % groups || keep <= 0 || keep > groups)
+    return zi_refuse("moe_route: %d outputs in %d groups of which %d are kept", NR, groups, keep);
+  if (top > keep * (NR / groups)) return zi_refuse("moe_route: %d outputs cannot be chosen from %d groups of %d", top, keep, NR / groups);
+  if (score_kind != 0 && score_kind != 1) return zi_refuse("moe_route: unknown score %d", score_kind);
+  const size_t smem = (size_t)ROUTE_WARPS * 3 * NR * sizeof(float);
+  if (smem > 48 * 1024) return zi_refuse("moe_route: %d router outputs are more than this kernel holds", NR);
+  zi_launch(moe_route_grouped_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream, chosen,
+            weight, logits, T, NR, top, renormalize, score_kind, groups, keep, wscale);
+  return zi_check_launch("moe_route_grouped");
 }
 
 extern "C" int zi_moe_router(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w, int w_dtype,

@@ -100,29 +100,45 @@ class DecoderModel:
     def cache_needs(self) -> tuple[dict[str, KVCacheNeed], dict[str, StateNeed]]:
         kv, state = {}, {}
         for run in self.runs:
-            need = self.blocks[run.layer].mixer.cache_need()
-            prev = kv.get(run.cache, state.get(run.cache))
-            if prev is not None and prev != need:
-                raise ValueError(f"cache {run.cache!r} is shared by layers with different needs: {prev} and {need}")
-            if isinstance(need, KVCacheNeed):
-                kv[run.cache] = need
-            elif isinstance(need, StateNeed):
-                state[run.cache] = need
-            elif need is not None:
-                raise TypeError(f"layer {run.layer}: unknown cache need {need!r}")
+            for name, need in self._needs_of(run).items():
+                prev = kv.get(name, state.get(name))
+                if prev is not None and prev != need:
+                    raise ValueError(f"cache {name!r} is shared by layers with different needs: {prev} and {need}")
+                if isinstance(need, KVCacheNeed):
+                    kv[name] = need
+                elif isinstance(need, StateNeed):
+                    state[name] = need
+                else:
+                    raise TypeError(f"layer {run.layer}: unknown cache need {need!r}")
         return kv, state
+
+    def _needs_of(self, run: Run) -> dict:
+        """The caches and states a run uses, by name.  A mixer needs one (named like the run's cache), none, or
+        several (a dictionary part -> need: a mixer of several branches; named ``<run's cache>.<part>``)."""
+        need = self.blocks[run.layer].mixer.cache_need()
+        if need is None:
+            return {}
+        if isinstance(need, dict):
+            return {f"{run.cache}.{part}": n for part, n in need.items() if n is not None}
+        return {run.cache: need}
+
+    def _view(self, storage: CacheStorage, name: str, writes: bool, kv: dict, state: dict):
+        if name in kv:
+            return storage.kv_view(name, writes)
+        if name in state:
+            return storage.state_view(name, writes)
+        return None
 
     def attach(self, storage: CacheStorage) -> None:
         """Binds every run to its view of the cache storage."""
         kv, state = self.cache_needs()
         self._views = []
         for run in self.runs:
-            if run.cache in kv:
-                self._views.append(storage.kv_view(run.cache, run.writes))
-            elif run.cache in state:
-                self._views.append(storage.state_view(run.cache, run.writes))
+            need = self.blocks[run.layer].mixer.cache_need()
+            if isinstance(need, dict):     # a mixer of several branches gets its views by the branches' names
+                self._views.append({part: self._view(storage, f"{run.cache}.{part}", run.writes, kv, state) for part in need})
             else:
-                self._views.append(None)
+                self._views.append(self._view(storage, run.cache, run.writes, kv, state))
 
     # ------------------------------------------------------------------ forward
     def forward(self, step, argmax: bool = False):

@@ -160,8 +160,18 @@ class Scaled:
         return self.delta.shape
 
 
+class Carried:
+    """Nothing is pending: the residual stream is up to date, and ``x`` is that stream in the activations' type (a block
+    that made it hands it to the next one, which may read it instead of casting the stream again)."""
+
+    def __init__(self, x: torch.Tensor):
+        self.x = x
+
+
 def _unscaled(delta):
-    """(update, multiplier) of an update given plain or as :class:`Scaled`."""
+    """(update, multiplier) of an update given plain or as :class:`Scaled`; nothing for :class:`Carried`."""
+    if isinstance(delta, Carried):
+        return None, 1.0
     if isinstance(delta, Scaled):
         return delta.delta, delta.scale
     return delta, 1.0
@@ -319,11 +329,47 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: Optio
     return swiglu(gu, out_dtype=out_dtype or x.dtype, interleave=SWIGLU_INTERLEAVE, activation=activation)
 
 
-def rope_table(n_pos: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+def rope_table(n_pos: int, head_dim: int, theta: float, device, factor: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos and sin [positions, head_dim/2] of the angles position * theta^(-2i/head_dim) / factor (``factor``: linear
+    scaling of the positions; 1 for none)."""
     cos = torch.empty((n_pos, head_dim // 2), dtype=torch.float32, device=device)
     sin = torch.empty_like(cos)
-    _check(lib().zi_rope_table(_ptr(cos), _ptr(sin), n_pos, head_dim, ctypes.c_float(theta), _stream()), "rope_table")
+    _check(lib().zi_rope_table_scaled(_ptr(cos), _ptr(sin), n_pos, head_dim, ctypes.c_float(theta), ctypes.c_float(factor),
+                                      _stream()), "rope_table")
     return cos, sin
+
+
+def qk_prepare(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, rot_dims: int,
+               q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+               cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor,
+               k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], slots: Optional[torch.Tensor],
+               page_size: int, values_from_keys: bool = False, write_kv: bool = True) -> torch.Tensor:
+    """The general form of :func:`qk_norm_rope_store`: the rotation turns only the first ``rot_dims`` dimensions of a
+    head (pairs (i, i + rot_dims/2), tables [positions, rot_dims/2]), and with ``values_from_keys`` the rows are
+    [q heads | k heads] and a token's value is its key AS PROJECTED, before norm and rotation.  Rewrites q in place
+    and returns ``qkv``."""
+    T = qkv.shape[0]
+    width = (num_heads + ((1 if values_from_keys else 2) * num_kv_heads if write_kv else 0)) * head_dim
+    _need(qkv.stride(1) == 1 and qkv.shape[1] >= width, "qk_prepare: dense rows as wide as their heads")
+    for wt in (q_weight, k_weight):
+        if wt is not None:
+            _need(wt.dtype == torch.float32 and wt.numel() == head_dim, "q/k norm weights are float32 [head_dim]")
+    n_table = 0
+    if cos is not None:
+        _need(cos.shape == sin.shape and cos.shape[1] == rot_dims // 2 and cos.dtype == torch.float32,
+              "rotary tables are float32 [positions, rot_dims/2]")
+        n_table = cos.shape[0]
+    _i32(positions, "positions")
+    if write_kv:
+        _need(k_cache is not None and v_cache is not None and slots is not None, "writing needs pages and slots")
+        _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype, "cache pages have the activations' dtype")
+        _i32(slots, "slots")
+    with _prof.region("qk_prepare (norm, partial rotation, page write)", lambda: 2 * T * width * qkv.element_size()):
+        _check(lib().zi_qk_prepare(_ptr(qkv), _tag(qkv), T, qkv.stride(0), _ptr(qkv), qkv.stride(0), num_heads, num_kv_heads,
+                                   head_dim, rot_dims, _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps), _ptr(cos), _ptr(sin),
+                                   n_table, _ptr(positions), _ptr(k_cache), _ptr(v_cache), _ptr(slots), page_size,
+                                   1 if values_from_keys else 0, 1 if write_kv else 0, _stream()), "qk_prepare")
+    return qkv
 
 
 def qk_norm_rope_store(qkv, num_heads: int, num_kv_heads: int, head_dim: int,
@@ -890,8 +936,9 @@ def attention_tile_rows() -> int:
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
                     cu_q: torch.Tensor, kv_lens: torch.Tensor, tile_seq: torch.Tensor, tile_q0: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
-                    scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Causal attention of the step's query tokens over their requests' pages.
+                    scale: float, out: Optional[torch.Tensor] = None, sink: float = 0.0) -> torch.Tensor:
+    """Causal attention of the step's query tokens over their requests' pages.  ``sink``: that many keys of
+    score 0 without a value are counted in the softmax's denominator (p_j = exp(s_j) / (sink + sum exp(s))).
 
     ``q`` [T, >= num_heads*head_dim] (row stride free), caches [pages, kv heads,
     page_size, head_dim], ``block_tables`` [n, W], ``cu_q`` [n+1] token offsets,
@@ -908,11 +955,11 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     if out is None:
         out = torch.empty((T, num_heads * head_dim), dtype=q.dtype, device=q.device)
     with _prof.region("attention (exact, CUDA cores)"):
-        _check(lib().zi_paged_attention(
+        _check(lib().zi_paged_attention_sink(
             _ptr(out), out.stride(0), _ptr(q), q.stride(0), _tag(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
             block_tables.stride(0), _ptr(cu_q), _ptr(kv_lens), _ptr(tile_seq), _ptr(tile_q0), tile_seq.shape[0],
-            num_heads, num_kv_heads, head_dim, page_size, int(window or 0), ctypes.c_float(scale), _stream()),
-            "paged_attention")
+            num_heads, num_kv_heads, head_dim, head_dim, head_dim, page_size, int(window or 0), ctypes.c_float(scale),
+            0, 0, ctypes.c_float(sink), _stream()), "paged_attention")
     return out
 
 
@@ -942,7 +989,7 @@ def attention_prefill_tile_rows() -> int:
 
 def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor, step,
               num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
-              scale: float) -> torch.Tensor:
+              scale: float, sink: float = 0.0) -> torch.Tensor:
     """Attention of a step's query tokens over their pages, by the fastest kernel that
     takes the shape: in bfloat16 with head sizes 64/128 (decode also 256) the
     tensor-core kernels (requests that bring one token go to the split-key decode
@@ -954,9 +1001,10 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
     dec_ok = fast and step.n_dec > 0 and L.zi_attention_mma_supported(num_heads, num_kv_heads, head_dim, 1)
     pf_ok = fast and step.n_pf_tiles > 0 and L.zi_attention_mma_supported(num_heads, num_kv_heads, head_dim, 0) \
         and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
-    if (step.n_dec > 0 and not dec_ok) or (step.n_pf_tiles > 0 and not pf_ok):
+    if sink or (step.n_dec > 0 and not dec_ok) or (step.n_pf_tiles > 0 and not pf_ok):
+        # a softmax with a sink runs on the exact kernel (the tensor-core kernels have the plain softmax)
         return paged_attention(q, k_cache, v_cache, block_tables, step.cu_q, step.kv_lens, step.tile_seq, step.tile_q0,
-                               num_heads, num_kv_heads, head_dim, page_size, window, scale)
+                               num_heads, num_kv_heads, head_dim, page_size, window, scale, sink=sink)
     _need(q.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous(), "attention: dense operands")
     _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim) and k_cache.dtype == q.dtype,
           "cache pages are [pages, kv heads, page, d] in the activations' dtype")
@@ -1092,6 +1140,199 @@ def attention_decode_fused(qkv, num_heads: int, num_kv_heads: int, head_dim: int
             _ptr(step.kv_lens), _ptr(step.dec_seq), step.n_dec, num_heads, num_kv_heads, head_dim, page_size,
             int(window or 0), ctypes.c_float(scale), splits, _stream()), "attention (fused decode)")
     return out
+
+
+# ------------------------------------------------- norm of a sublayer's output, small elementwise
+def _whole(delta, dtype=torch.float32):
+    """(tensor, multiplier) of an update given as a tensor, :class:`Partials` or :class:`Scaled`."""
+    delta, scale = _unscaled(delta)
+    if isinstance(delta, Partials):
+        delta = delta.sum(dtype)
+    return delta, scale
+
+
+def norm_residual(h: torch.Tensor, a, weight: torch.Tensor, eps: float, out_dtype: torch.dtype, b=None) -> torch.Tensor:
+    """``h += rmsnorm(a + b) * weight`` in place, the norm taken over the sublayer's OUTPUT (``a``, and ``b`` if given:
+    tensors, :class:`Partials`, or either inside :class:`Scaled`).  Returns ``h`` in ``out_dtype``: what the next
+    sublayer reads (``h`` itself for float32)."""
+    T, H = h.shape
+    a, sa = _whole(a)
+    b, sb = _whole(b) if b is not None else (None, 0.0)
+    _need(h.dtype == torch.float32 and h.is_contiguous(), "the residual stream is contiguous float32")
+    _need(weight.dtype == torch.float32 and weight.numel() == H, "norm weight must be float32 of the row's width")
+    for t in (a, b):
+        if t is not None:
+            _need(tuple(t.shape) == (T, H) and t.is_contiguous(), "an update must match the residual stream")
+    x = None if out_dtype == torch.float32 else torch.empty((T, H), dtype=out_dtype, device=h.device)
+    with _prof.region("norm of the output + residual add", lambda: 2 * _nb(h) + 2 * _nb(a, b) + _nb(x)):
+        _check(lib().zi_norm_residual(_ptr(h), _ptr(a), _tag(a), ctypes.c_float(sa), _ptr(b), _tag(b) if b is not None else F32,
+                                      ctypes.c_float(sb), _ptr(weight), ctypes.c_float(eps), _ptr(x),
+                                      _tag(x) if x is not None else F32, T, H, _stream()), "norm_residual")
+    return h if x is None else x
+
+
+def cast_rows(h: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The 32-bit residual stream in the activations' type (itself for float32)."""
+    if dtype == torch.float32:
+        return h
+    _need(h.dtype == torch.float32 and h.is_contiguous(), "cast_rows: contiguous float32")
+    out = torch.empty(h.shape, dtype=dtype, device=h.device)
+    with _prof.region("cast", lambda: _nb(h, out)):
+        _check(lib().zi_cast_rows(_ptr(out), _tag(out), _ptr(h), ctypes.c_longlong(h.numel()), _stream()), "cast_rows")
+    return out
+
+
+def relu2_(x: torch.Tensor) -> torch.Tensor:
+    """``x = relu(x)^2`` in place."""
+    _need(x.is_contiguous(), "relu2: a contiguous tensor")
+    with _prof.region("relu2", lambda: 2 * _nb(x)):
+        _check(lib().zi_relu2(_ptr(x), _tag(x), ctypes.c_longlong(x.numel()), _stream()), "relu2")
+    return x
+
+
+# ------------------------------------------- mixers with a matrix-valued state per head
+def _slot_view(state: torch.Tensor, name: str):
+    """(tensor, elements from one slot to the next) of a float32 per-request state that may be a view of wider rows."""
+    _need(state.dtype == torch.float32 and state.dim() >= 2 and all(
+        state.stride(i) == state.stride(i + 1) * state.shape[i + 1] for i in range(1, state.dim() - 1)) and state.stride(-1) == 1,
+        f"{name}: a float32 state whose slots are dense")
+    return state, state.stride(0)
+
+
+def short_conv(x: torch.Tensor, kernel: torch.Tensor, tail: torch.Tensor, step, activation: Optional[str] = "silu") -> torch.Tensor:
+    """Causal convolution per channel over the last ``taps`` tokens of each request: ``x`` [T, C] (rows may be views of
+    wider rows), ``kernel`` float32 [C, taps] (last column: the current token), no bias; the inputs before a
+    request's first token of this step come from ``tail`` [slots, taps-1, C] (oldest first; zero at a request's
+    start).  Returns float32 [T, C], with ``silu`` applied if asked.  The tail is left as it is
+    (:func:`short_conv_carry` moves it on, after every reader of the old one)."""
+    T, C = x.shape
+    taps = kernel.shape[1]
+    tail, stride = _slot_view(tail, "short_conv")
+    _need(x.stride(1) == 1 and kernel.dtype == torch.float32 and kernel.is_contiguous() and kernel.shape[0] == C
+          and tuple(tail.shape[1:]) == (max(taps - 1, 0), C), "short_conv: kernel float32 [C, taps], tail [slots, taps-1, C]")
+    _need(activation in (None, "silu"), f"short_conv: unknown activation {activation!r}")
+    y = torch.empty((T, C), dtype=torch.float32, device=x.device)
+    with _prof.region("short convolution", lambda: T * C * (x.element_size() * taps + 4)):
+        _check(lib().zi_short_conv(_ptr(y), y.stride(0), _ptr(x), x.stride(0), _tag(x), _ptr(kernel), _ptr(tail), _ll(stride), C,
+                                   taps, 1 if activation == "silu" else 0, _ptr(step.cu_q), _ptr(step.state_slots), step.n_seqs,
+                                   T, _stream()), "short_conv")
+    return y
+
+
+def short_conv_carry(x: torch.Tensor, taps: int, tail: torch.Tensor, step) -> None:
+    """Moves ``tail`` on to the last ``taps - 1`` inputs of every request after this step's tokens."""
+    T, C = x.shape
+    if taps <= 1:
+        return
+    tail, stride = _slot_view(tail, "short_conv_carry")
+    _need(x.stride(1) == 1 and tuple(tail.shape[1:]) == (taps - 1, C), "short_conv_carry: tail [slots, taps-1, C]")
+    with _prof.region("short convolution (carry)", lambda: 2 * step.n_seqs * (taps - 1) * C * 4):
+        _check(lib().zi_short_conv_carry(_ptr(tail), _ll(stride), _ptr(x), x.stride(0), _tag(x), C, taps, _ptr(step.cu_q),
+                                         _ptr(step.state_slots), step.n_seqs, _stream()), "short_conv_carry")
+
+
+def decay_sigmoid_root_(z: torch.Tensor, bias: Optional[torch.Tensor], tau: float) -> torch.Tensor:
+    """In place on float32 [T, N]: ``sigmoid(z + bias)^(1/tau)``, as ``exp(log_sigmoid(z + bias) / tau)``."""
+    _need(z.dtype == torch.float32 and z.is_contiguous(), "decay: contiguous float32")
+    N = z.shape[-1]
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == N, "decay: bias float32 [N]")
+    with _prof.region("decay", lambda: 2 * _nb(z)):
+        _check(lib().zi_decay(_ptr(z), _ll(z.numel() // N), N, N, _ptr(bias), None, ctypes.c_float(1.0 / tau), 0, _stream()), "decay")
+    return z
+
+
+def decay_exp_softplus_(z: torch.Tensor, bias: Optional[torch.Tensor], a_log: torch.Tensor, head_dim: int) -> torch.Tensor:
+    """In place on float32 [T, heads * head_dim]: ``exp(-exp(a_log[head]) * softplus(z + bias))``."""
+    _need(z.dtype == torch.float32 and z.is_contiguous(), "decay: contiguous float32")
+    N = z.shape[-1]
+    _need(a_log.dtype == torch.float32 and a_log.numel() * head_dim == N, "decay: a_log float32 [heads]")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == N, "decay: bias float32 [N]")
+    with _prof.region("decay", lambda: 2 * _nb(z)):
+        _check(lib().zi_decay(_ptr(z), _ll(z.numel() // N), N, head_dim, _ptr(bias), _ptr(a_log), ctypes.c_float(1.0), 1,
+                              _stream()), "decay")
+    return z
+
+
+def unit_norm_(x: torch.Tensor, heads: int, head_dim: int, eps: float, scale: float = 1.0) -> torch.Tensor:
+    """In place on float32 rows [T, >= heads * head_dim]: every head ``scale * x / sqrt(sum(x^2) + eps)``."""
+    _need(x.dtype == torch.float32 and x.stride(1) == 1 and x.shape[1] >= heads * head_dim, "unit_norm: float32 rows")
+    with _prof.region("unit norm", lambda: 2 * x.shape[0] * heads * head_dim * 4):
+        _check(lib().zi_unit_norm(_ptr(x), x.stride(0), x.shape[0], heads, head_dim, ctypes.c_float(eps), ctypes.c_float(scale),
+                                  _stream()), "unit_norm")
+    return x
+
+
+def sigmoid_rows(x: torch.Tensor) -> torch.Tensor:
+    """float32 ``sigmoid(x)`` of [T, W] rows that may be views of wider rows."""
+    T, W = x.shape
+    _need(x.stride(1) == 1, "sigmoid_rows: dense rows")
+    out = torch.empty((T, W), dtype=torch.float32, device=x.device)
+    with _prof.region("sigmoid", lambda: T * W * (4 + x.element_size())):
+        _check(lib().zi_sigmoid_rows(_ptr(out), W, _ptr(x), x.stride(0), _tag(x), T, W, _stream()), "sigmoid_rows")
+    return out
+
+
+def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, beta: Optional[torch.Tensor],
+                      q_scale: float, state: torch.Tensor, heads: int, key_heads: int, dim: int, vdim: int, step) -> torch.Tensor:
+    """Per request and head, over the step's tokens, from and to ``state`` [slots, heads, dim, vdim] (float32):
+    ``S = diag(decay_t) S``; ``u = v_t`` or, with ``beta``, ``beta_t (v_t - S^T k_t)`` (the delta rule);
+    ``S += k_t u^T``; ``o_t = S^T (q_scale q_t)``.  ``q``, ``k`` [T, key_heads * dim] (head h reads key head
+    h // (heads / key_heads)), ``v`` [T, heads * vdim], ``decay`` float32 [T, heads * dim], ``beta`` float32 [T, heads];
+    rows may be views of wider rows.  Returns float32 [T, heads * vdim]."""
+    T = q.shape[0]
+    state, stride = _slot_view(state, "linear_recurrence")
+    _need(state[0].numel() == heads * dim * vdim, "linear_recurrence: state [slots, heads, dim, vdim]")
+    _need(q.dtype == k.dtype and q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1
+          and q.shape[1] == key_heads * dim and k.shape[1] == key_heads * dim and v.shape[1] == heads * vdim,
+          "linear_recurrence: q, k [T, key heads * dim], v [T, heads * vdim] with dense rows")
+    _need(decay.dtype == torch.float32 and decay.stride(1) == 1 and decay.shape[1] == heads * dim, "linear_recurrence: decay")
+    if beta is not None:
+        _need(beta.dtype == torch.float32 and beta.stride(1) == 1 and beta.shape[1] == heads, "linear_recurrence: beta")
+    out = torch.empty((T, heads * vdim), dtype=torch.float32, device=q.device)
+    with _prof.region("linear recurrence" + (" (delta rule)" if beta is not None else ""),
+                      lambda: _nb(q, k, v, decay, out) + 2 * step.n_seqs * heads * dim * vdim * 4, 6 * T * heads * dim * vdim):
+        _check(lib().zi_linear_recurrence(
+            _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _tag(q), _ptr(v), v.stride(0), _tag(v),
+            _ptr(decay), decay.stride(0), _ptr(beta), beta.stride(0) if beta is not None else 0, ctypes.c_float(q_scale),
+            _ptr(state), _ll(stride), heads, key_heads, dim, vdim, 1 if beta is not None else 0, _ptr(step.cu_q),
+            _ptr(step.state_slots), step.n_seqs, _stream()), "linear_recurrence")
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: torch.Tensor, gate_kind: str, heads: int, vdim: int,
+                   out_dtype: torch.dtype) -> torch.Tensor:
+    """Every head of float32 ``o`` [T, heads * vdim] divided by its root mean square (``eps`` inside the root), times
+    ``weight`` [vdim], times ``silu(gate)`` or ``sigmoid(gate)`` (``gate`` [T, heads * vdim], rows may be views)."""
+    T = o.shape[0]
+    _need(o.dtype == torch.float32 and o.is_contiguous() and gate.stride(1) == 1 and gate.shape[1] == heads * vdim
+          and weight.dtype == torch.float32 and weight.numel() == vdim, "head_norm_gate: shapes")
+    _need(gate_kind in ("silu", "sigmoid"), f"head_norm_gate: unknown gate {gate_kind!r}")
+    out = torch.empty((T, heads * vdim), dtype=out_dtype, device=o.device)
+    with _prof.region("head norm + gate", lambda: _nb(o, out) + T * heads * vdim * gate.element_size()):
+        _check(lib().zi_head_norm_gate(_ptr(out), _tag(out), out.stride(0), _ptr(o), o.stride(0), _ptr(weight), ctypes.c_float(eps),
+                                       _ptr(gate), _tag(gate), gate.stride(0), 0 if gate_kind == "silu" else 1, T, heads, vdim,
+                                       _stream()), "head_norm_gate")
+    return out
+
+
+def moe_route_grouped(logits: torch.Tensor, top: int, score: str = "sigmoid", groups: int = 1, keep: int = 1,
+                      scale: float = 1.0, renormalize: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per token: scores ``sigmoid(z)`` or ``softmax(z)``; the outputs form ``groups`` equal groups of neighbours, a
+    group's score is the sum of its two largest scores, and the ``top`` largest scores are chosen among the outputs of
+    the ``keep`` best groups (int32 [T, top]); their weights are the scores times ``scale`` (float32 [T, top]),
+    divided by the chosen scores' sum first if ``renormalize``."""
+    T, NR = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "router logits are contiguous float32")
+    _need(score in ("softmax", "sigmoid"), f"unknown router score {score!r}")
+    chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weight = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    with _prof.region("moe route (groups)", lambda: _nb(logits, chosen, weight)):
+        _check(lib().zi_moe_route_grouped(_ptr(chosen), _ptr(weight), _ptr(logits), T, NR, top, 1 if renormalize else 0,
+                                          1 if score == "sigmoid" else 0, groups, keep, ctypes.c_float(scale), _stream()),
+               "moe_route_grouped")
+    return chosen, weight
 
 
 # ------------------------------------------------------------------------ sampling

@@ -1,10 +1,11 @@
 from .base import (Block, BuildContext, FeedForward, KVCacheNeed, Mixer, Norm, Part, PositionEncoding, StateNeed,
                    TensorSpec, make_part, prefixed, register_part, take, unregister_part)
 from .attention import GQAttention
-from .block import PreNormBlock
+from .block import OutputNormBlock, PreNormBlock
 from .embedding import LMHead, TokenEmbedding
 from .latent_attention import LatentAttention
-from .mlp import SwiGLUMLP
+from .linear_attention import GatedDeltaRule, GatedLinearAttention, ParallelMixer
+from .mlp import PlainMLP, SwiGLUMLP
 from .moe import RoutedExperts
 from .norm import RMSNorm
 from .rglru import RGLRUMixer
@@ -13,11 +14,14 @@ from .rope import NoPosition, RotaryPosition
 for _kind, _cls in (("rmsnorm", RMSNorm), ("rope", RotaryPosition), ("no_position", NoPosition),
                     ("gqa_attention", GQAttention), ("swiglu_mlp", SwiGLUMLP), ("prenorm_block", PreNormBlock),
                     ("token_embedding", TokenEmbedding), ("lm_head", LMHead), ("latent_attention", LatentAttention),
-                    ("rglru", RGLRUMixer), ("routed_experts", RoutedExperts)):
+                    ("rglru", RGLRUMixer), ("routed_experts", RoutedExperts), ("outnorm_block", OutputNormBlock),
+                    ("plain_mlp", PlainMLP), ("gated_linear_attention", GatedLinearAttention),
+                    ("gated_delta_rule", GatedDeltaRule), ("parallel_mixer", ParallelMixer)):
     register_part(_kind, _cls, replace=True)
 
 __all__ = [
-    "Block", "BuildContext", "FeedForward", "GQAttention", "KVCacheNeed", "LMHead", "LatentAttention", "Mixer",
+    "Block", "BuildContext", "FeedForward", "GQAttention", "GatedDeltaRule", "GatedLinearAttention", "OutputNormBlock",
+    "ParallelMixer", "PlainMLP", "KVCacheNeed", "LMHead", "LatentAttention", "Mixer",
     "NoPosition", "Norm", "Part", "PositionEncoding", "PreNormBlock", "RGLRUMixer", "RMSNorm", "RotaryPosition",
     "RoutedExperts", "StateNeed", "SwiGLUMLP", "TensorSpec",
     "TokenEmbedding", "make_part", "prefixed", "register_part", "take", "unregister_part",

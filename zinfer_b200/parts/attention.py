@@ -8,6 +8,12 @@ its position (within ``window`` if one is set); softmax of dot * 1/sqrt(d) in
 (src/model/runtime/optimized_decoder/layer.zig:110-142,188;
 src/model/layers/gqa_attention/spec.zig:3-26; src/kernel/attention/basic.zig:27-76.)
 The head size is independent of the model width.
+
+Options beyond that form (each switches the mixer to the general kernels; all default to the form above):
+``scale`` replaces 1/sqrt(d); ``sink`` s counts s keys of score 0 without a value in the softmax's denominator
+(p_j = exp(s_j) / (s + sum exp)); ``values: "keys"`` has no value projection, a token's value is its key as
+projected, before norm and rotation; a position part whose ``head_dim`` is smaller than the head rotates only
+the head's first dimensions; ``names`` gives the tensors' names (q, k, v, o, q_norm, k_norm).
 """
 from __future__ import annotations
 
@@ -35,31 +41,50 @@ class GQAttention(Mixer):
         self.position = make_part(params["position"], ctx) if params.get("position") is not None else None
         # 1/sqrt(d) as a 32-bit value, applied to the score after the dot (basic.zig:50)
         self.scale = float(np.float32(1.0) / np.sqrt(np.float32(self.d)))
+        if params.get("scale") is not None:
+            self.scale = float(params["scale"])
+        self.sink = float(params.get("sink", 0.0))
+        self.values_from_keys = params.get("values", "projection") == "keys"
+        if params.get("values", "projection") not in ("projection", "keys"):
+            raise ValueError(f"values come from a projection or from the keys, not {params['values']!r}")
+        self.rot_dims = int(getattr(self.position, "head_dim", self.d)) if self.position is not None else 0
+        if self.rot_dims > self.d:
+            raise ValueError(f"{self.rot_dims} rotated dimensions do not fit a head of {self.d}")
+        names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+                 "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+        names.update(params.get("names") or {})
+        self.names = names
+        # what the fused kernels (norm + rotation of the whole head, plain softmax, values of their own) do not take
+        self.general = bool(self.sink or self.values_from_keys
+                            or (self.position is not None and self.rot_dims != self.d and hasattr(self.position, "head_dim")))
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
 
     # ------------------------------------------------------------------ weights
     def tensor_specs(self):
         q, kv = self.nq * self.d, self.nkv * self.d
+        n = self.names
         specs = {
-            "q_proj.weight": TensorSpec((q, self.hidden)),
-            "k_proj.weight": TensorSpec((kv, self.hidden)),
-            "v_proj.weight": TensorSpec((kv, self.hidden)),
-            "o_proj.weight": TensorSpec((self.hidden, q)),
+            n["q"]: TensorSpec((q, self.hidden)),
+            n["k"]: TensorSpec((kv, self.hidden)),
+            n["o"]: TensorSpec((self.hidden, q)),
         }
+        if not self.values_from_keys:
+            specs[n["v"]] = TensorSpec((kv, self.hidden))
         if self.qk_norm_eps is not None:
-            specs["q_norm.weight"] = TensorSpec((self.d,), init="norm")
-            specs["k_norm.weight"] = TensorSpec((self.d,), init="norm")
+            specs[n["q_norm"]] = TensorSpec((self.d,), init="norm")
+            specs[n["k_norm"]] = TensorSpec((self.d,), init="norm")
         return specs
 
     def bind(self, tensors):
-        parts = [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]]
+        n = self.names
+        parts = [tensors[n["q"]], tensors[n["k"]]] + ([] if self.values_from_keys else [tensors[n["v"]]])
         if len({p.dtype for p in parts}) > 1:
             parts = [p.to(torch.float32) for p in parts]
         self.w_qkv = torch.cat(parts, dim=0).contiguous()
-        self.w_o = tensors["o_proj.weight"].contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
         if self.qk_norm_eps is not None:
-            self.q_norm = tensors["q_norm.weight"].to(torch.float32).contiguous()
-            self.k_norm = tensors["k_norm.weight"].to(torch.float32).contiguous()
+            self.q_norm = tensors[n["q_norm"]].to(torch.float32).contiguous()
+            self.k_norm = tensors[n["k_norm"]].to(torch.float32).contiguous()
 
     # -------------------------------------------------------------------- cache
     def cache_need(self):
@@ -69,7 +94,23 @@ class GQAttention(Mixer):
         return None if self.position is None else getattr(self.position, "n_positions", None)
 
     # ------------------------------------------------------------------ forward
+    def heads_out(self, x, step, cache):
+        """The attention's heads [T, num_heads * d] before the output projection, by the general kernels."""
+        q_width = self.nq * self.d
+        w = self.w_qkv if cache.writes else self.w_qkv[:q_width]
+        qkv = ops.linear(x, w, out_dtype=self.ctx.dtype)
+        group = step.kv_groups[cache.group]
+        cos, sin = self.position.tables() if self.position is not None else (None, None)
+        q = ops.qk_prepare(qkv, self.nq, self.nkv, self.d, self.rot_dims, self.q_norm, self.k_norm,
+                           self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos, sin, step.positions,
+                           cache.k, cache.v, group.slot_mapping, cache.page_size,
+                           values_from_keys=self.values_from_keys, write_kv=cache.writes)
+        return ops.attention(q, cache.k, cache.v, group.block_tables, step, self.nq, self.nkv, self.d,
+                             cache.page_size, self.window, self.scale, sink=self.sink)
+
     def forward(self, x, step, cache):
+        if self.general:
+            return ops.linear(self.heads_out(x, step, cache), self.w_o, out_dtype=self.ctx.dtype, allow_partials=True)
         q_width = self.nq * self.d
         w = self.w_qkv if cache.writes else self.w_qkv[:q_width]  # a reader of another's cache needs q only
         qkv = ops.linear(x, w, out_dtype=self.ctx.dtype, allow_partials=True)

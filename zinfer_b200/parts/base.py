@@ -39,12 +39,24 @@ class TensorSpec:
     """A tensor a part needs.  ``init`` says how the random-weights mode fills it:
     ``matrix`` normal(0, 0.02), ``norm`` 1 + U(-0.1, 0.1), ``zeros``; ``integer``
     tensors are kept as int32, others in the run's dtype (bfloat16 or float32)
-    unless the file stores them in 32-bit, in which case they stay so."""
+    unless the file stores them in 32-bit, in which case they stay so.
+
+    A dimension of -1 is free: the file gives it (the rank of a low-rank pair of matrices that no
+    configuration key names); the part reads it from the tensor it is bound to.  ``free`` is the size the
+    random-weights mode gives such a dimension."""
 
     shape: tuple[int, ...]
     init: str = "matrix"
     optional: bool = False
     integer: bool = False
+    free: int = 16
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(a == -1 and b > 0 or a == b for a, b in zip(self.shape, shape))
+
+    def concrete(self) -> tuple[int, ...]:
+        return tuple(self.free if a == -1 else a for a in self.shape)
 
 
 @dataclass(frozen=True)

@@ -56,3 +56,37 @@ class PreNormBlock(Block):
             return a
         x = self.ffn_norm.forward(h, a)
         return self._update(self.feed_forward.forward(x))
+
+
+class OutputNormBlock(PreNormBlock):
+    """The arrangement that norms a sublayer's OUTPUT: h1 = h + norm1(mixer(h)); h2 = h1 + norm2(ffn(h1)).
+    The sublayers read the residual stream itself (in the activations' type).  Same parameters and tensor
+    names as :class:`PreNormBlock`; ``residual_scale`` multiplies the normed update's input, which the norm
+    undoes, so it is refused unless 1.
+
+    Nothing is left pending: the norm's kernel adds the normed output into ``h`` and hands back ``h`` in the
+    activations' type, which the next sublayer (or, as :class:`ops.Carried`, the next block) reads."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        if self.residual_scale != 1.0:
+            raise ValueError("a block that norms its sublayers' outputs takes no residual multiplier")
+
+    def forward(self, h, pending, step, cache, bias=None):
+        if bias is not None:
+            raise ValueError("a block that norms its sublayers' outputs takes no per-pass vector")
+        if isinstance(pending, ops.Carried):
+            x = pending.x
+        else:
+            if pending is not None:
+                ops.residual_add(h, pending)
+            x = ops.cast_rows(h, self.ctx.dtype)
+        mixed = self.mixer.forward(x, step, cache)
+        a, b = mixed if isinstance(mixed, tuple) else (mixed, None)        # a mixer of two branches hands back both
+        x = ops.norm_residual(h, a, self.mixer_norm.weight, self.mixer_norm.eps, self.ctx.dtype, b=b)
+        if self.feed_forward is None:
+            return ops.Carried(x)
+        out = self.feed_forward.forward(x)
+        a, b = out if isinstance(out, tuple) else (out, None)              # routed experts beside a shared one
+        x = ops.norm_residual(h, a, self.ffn_norm.weight, self.ffn_norm.eps, self.ctx.dtype, b=b)
+        return ops.Carried(x)

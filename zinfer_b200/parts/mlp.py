@@ -49,3 +49,29 @@ class SwiGLUMLP(FeedForward):
             act = ops.swiglu(gu, out_dtype=self.ctx.dtype, activation=self.activation)
         # the product may come back as split-K partial sums; the next norm adds them with the residual
         return ops.linear(act, self.w_down, out_dtype=self.ctx.dtype, allow_partials=True)
+
+
+class PlainMLP(FeedForward):
+    """Dense feed-forward without a gate: down(act(up(x))), act = the square of relu (``relu2``).  ``names`` gives the
+    two tensors' names (up, down)."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.activation = str(params.get("activation", "relu2"))
+        if self.activation != "relu2":
+            raise ValueError(f"an ungated feed-forward with activation {self.activation!r} is not built (relu2 is)")
+        self.names = tuple(params.get("names", ("up", "down")))
+
+    def tensor_specs(self):
+        up, down = self.names
+        return {up: TensorSpec((self.inter, self.hidden)), down: TensorSpec((self.hidden, self.inter))}
+
+    def bind(self, tensors):
+        self.w_up = tensors[self.names[0]].contiguous()
+        self.w_down = tensors[self.names[1]].contiguous()
+
+    def forward(self, x):
+        mid = ops.relu2_(ops.linear(x, self.w_up, out_dtype=self.ctx.dtype))
+        return ops.linear(mid, self.w_down, out_dtype=self.ctx.dtype, allow_partials=True)

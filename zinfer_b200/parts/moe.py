@@ -8,6 +8,13 @@ s without the correction, divided by their sum only if ``renormalize``.  The las
 outputs stand for experts without weights whose output is their input.  An expert is
 W_down act(W_up h) with act the square of relu (``relu2``).
 
+Other routers and experts, by parameter: ``score: sigmoid`` scores each output alone, s = sigmoid(z);
+``groups`` / ``groups_kept`` cut the experts into equal groups of neighbours, score a group by the sum of its two
+largest scores and let only experts of the best groups be chosen; ``weight_scale`` multiplies the weights;
+``activation: silu_gated`` makes an expert W_down (silu(W_gate h) * (W_up h)); ``shared`` (a feed-forward part) runs
+for every token beside the routed experts, and ``forward`` then hands back the pair (routed, shared) for the block
+to add.
+
 The chosen (token, expert) pairs are laid out by expert on the device, in whole tiles, and two
 grouped products run over them; nothing is read back, so a decode step can be captured.
 """
@@ -30,10 +37,28 @@ class RoutedExperts(FeedForward):
         self.renormalize = bool(params.get("renormalize", False))
         self.has_correction = bool(params.get("correction", False))
         act = params.get("activation", "relu2")
-        if act != "relu2":
-            raise ValueError(f"experts with activation {act!r} are not built (relu2 is)")
-        if params.get("score", "softmax") != "softmax":
-            raise ValueError("router scores other than softmax are not built")
+        if act not in ("relu2", "silu_gated"):
+            raise ValueError(f"experts with activation {act!r} are not built (relu2 and silu_gated are)")
+        self.gated = act == "silu_gated"
+        self.score = params.get("score", "softmax")
+        if self.score not in ("softmax", "sigmoid"):
+            raise ValueError(f"router scores are softmax or sigmoid, not {self.score!r}")
+        self.groups = int(params.get("groups", 1))
+        self.groups_kept = int(params.get("groups_kept", self.groups))
+        self.weight_scale = float(params.get("weight_scale", 1.0))
+        # the fused router kernel has the softmax over all outputs; everything else takes the general choice
+        self.general_route = self.score != "softmax" or self.groups > 1 or self.weight_scale != 1.0
+        if self.general_route:
+            if self.identity or self.has_correction:
+                raise ValueError("identity experts and a correction are built for the softmax router without groups only")
+            if self.groups <= 0 or self.experts % self.groups or not 1 <= self.groups_kept <= self.groups:
+                raise ValueError(f"{self.experts} experts do not form {self.groups} groups of which {self.groups_kept} are kept")
+            if self.top > self.groups_kept * (self.experts // self.groups):
+                raise ValueError(f"{self.top} experts cannot be chosen from {self.groups_kept} groups of {self.experts // self.groups}")
+        from .base import make_part
+        self.shared = make_part(params["shared"], ctx) if params.get("shared") is not None else None
+        self.shared_name = params.get("shared_name", "shared.")
+        self.gate_name = params.get("gate_name", "gate")
         self.outputs = self.experts + self.identity
         if not 1 <= self.top <= self.outputs:
             raise ValueError(f"{self.top} of {self.outputs} router outputs cannot be chosen")
@@ -47,24 +72,52 @@ class RoutedExperts(FeedForward):
             specs["correction"] = TensorSpec((self.outputs,), init="zeros")
         for e in range(self.experts):
             p = self.expert_names.format(e)
+            if self.gated:
+                specs[p + self.gate_name] = TensorSpec((self.inter, self.hidden))
             specs[p + "up"] = TensorSpec((self.inter, self.hidden))
             specs[p + "down"] = TensorSpec((self.hidden, self.inter))
+        if self.shared is not None:
+            from .base import prefixed
+            specs.update(prefixed(self.shared_name, self.shared.tensor_specs()))
         return specs
 
     def bind(self, tensors):
         self.w_router = tensors["router"].contiguous()
         self.correction = tensors["correction"].to(torch.float32).contiguous() if self.has_correction else None
         ups = [tensors[self.expert_names.format(e) + "up"] for e in range(self.experts)]
+        if self.gated:     # an expert's gate rows above its up rows: one product feeds both
+            gates = [tensors[self.expert_names.format(e) + self.gate_name] for e in range(self.experts)]
+            ups = [torch.cat([g, u] if g.dtype == u.dtype else [g.to(torch.float32), u.to(torch.float32)], dim=0)
+                   for g, u in zip(gates, ups)]
+        if self.shared is not None:
+            from .base import take
+            self.shared.bind(take(tensors, self.shared_name))
         downs = [tensors[self.expert_names.format(e) + "down"] for e in range(self.experts)]
         if len({t.dtype for t in ups + downs}) > 1:
             ups, downs = [t.to(torch.float32) for t in ups], [t.to(torch.float32) for t in downs]
         dev = self.w_router.device
-        self.w_up = torch.stack(ups).contiguous() if ups else torch.empty((0, self.inter, self.hidden), device=dev)
+        self.up_rows = (2 if self.gated else 1) * self.inter
+        self.w_up = torch.stack(ups).contiguous() if ups else torch.empty((0, self.up_rows, self.hidden), device=dev)
         self.w_down = torch.stack(downs).contiguous() if downs else torch.empty((0, self.hidden, self.inter), device=dev)
 
     def forward(self, x):
+        routed = self.routed(x)
+        if self.shared is None:
+            return routed
+        return routed, self.shared.forward(x)
+
+    def _act(self, mid2):
+        """Between an expert's two products, where the first one's kernel has not done it: the gate."""
+        return ops.swiglu(mid2, out_dtype=self.ctx.dtype, activation="silu") if self.gated else mid2
+
+    def routed(self, x):
         T = x.shape[0]
-        if self.hidden <= 32768:      # the router's product and the choice in one kernel (the row fits its shared memory)
+        relu2 = not self.gated
+        if self.general_route:
+            logits = ops.linear_cuda_cores(x, self.w_router, out_dtype=torch.float32)     # 32-bit multiply-adds
+            chosen, weight = ops.moe_route_grouped(logits, self.top, self.score, self.groups, self.groups_kept,
+                                                   self.weight_scale, self.renormalize)
+        elif self.hidden <= 32768:      # the router's product and the choice in one kernel (the row fits its shared memory)
             chosen, weight = ops.moe_router(x, self.w_router, self.correction, self.top, self.renormalize)
         else:
             logits = ops.linear_cuda_cores(x, self.w_router, out_dtype=torch.float32)     # 32-bit multiply-adds
@@ -78,21 +131,22 @@ class RoutedExperts(FeedForward):
             row_token, row_self, pair_row, tile_expert, n_tiles = ops.moe_align(chosen, self.experts, tile)
             rows = row_token.numel()
             xs = ops.gather_rows(x, row_token)
-            mid = torch.empty((rows, self.inter), dtype=self.ctx.dtype, device=x.device)
-            ops.linear_grouped_tensor(xs, self.w_up, mid, tile_expert, relu2=True, pairs=pairs)
+            mid = torch.empty((rows, self.up_rows), dtype=self.ctx.dtype, device=x.device)
+            ops.linear_grouped_tensor(xs, self.w_up, mid, tile_expert, relu2=relu2, pairs=pairs)
             y = torch.empty((rows, self.hidden), dtype=torch.float32, device=x.device)
-            ops.linear_grouped_tensor(mid, self.w_down, y, tile_expert, pairs=pairs)
+            ops.linear_grouped_tensor(self._act(mid), self.w_down, y, tile_expert, pairs=pairs)
             return ops.moe_combine(y, x, chosen, weight, pair_row, self.experts)
         tile = ops.MOE_TILE_ROWS if pairs > 16 * max(self.experts, 1) else ops.MOE_TILE_ROWS_SMALL
         row_token, row_self, pair_row, tile_expert, n_tiles = ops.moe_align(chosen, self.experts, tile)
         rows = row_token.numel()
-        mid = torch.empty((rows, self.inter), dtype=self.ctx.dtype, device=x.device)
+        mid = torch.empty((rows, self.up_rows), dtype=self.ctx.dtype, device=x.device)
         y = torch.empty((rows, self.hidden), dtype=torch.float32, device=x.device)
-        if tile == ops.MOE_TILE_ROWS_SMALL and ops.linear_few_rows_ok(x, self.w_up) and ops.linear_few_rows_ok(mid, self.w_down):
+        if tile == ops.MOE_TILE_ROWS_SMALL and ops.linear_few_rows_ok(x, self.w_up) \
+                and ops.linear_few_rows_ok(mid[:, :self.inter], self.w_down):
             # few rows per expert (a decode step): the experts' weights are streamed once, bound by memory
-            ops.linear_few_rows(x, self.w_up, mid, row_token, tile_expert, n_tiles, relu2=True)
-            ops.linear_few_rows(mid, self.w_down, y, row_self, tile_expert, n_tiles)
+            ops.linear_few_rows(x, self.w_up, mid, row_token, tile_expert, n_tiles, relu2=relu2)
+            ops.linear_few_rows(self._act(mid), self.w_down, y, row_self, tile_expert, n_tiles)
         else:
-            ops.linear_grouped(x, self.w_up, mid, row_token, tile_expert, n_tiles, tile, relu2=True)
-            ops.linear_grouped(mid, self.w_down, y, row_self, tile_expert, n_tiles, tile)
+            ops.linear_grouped(x, self.w_up, mid, row_token, tile_expert, n_tiles, tile, relu2=relu2)
+            ops.linear_grouped(self._act(mid), self.w_down, y, row_self, tile_expert, n_tiles, tile)
         return ops.moe_combine(y, x, chosen, weight, pair_row, self.experts)

@@ -1,7 +1,9 @@
 """Rotary position encoding, rotate-half pairing (i, i + d/2) over the whole head
 (src/kernel/attention/rope.zig:67-90).  The part owns the cos/sin table, built on
 the device by the reference's 32-bit recipe (rope.zig:25-35); equal parts share
-one table."""
+one table.  ``scaling_factor`` f (linear scaling) divides every frequency by f: the angles are those of
+position / f.  ``head_dim`` is the number of dimensions the rotation turns, which a mixer may make
+smaller than its heads."""
 from __future__ import annotations
 
 from .. import ops
@@ -13,17 +15,20 @@ class RotaryPosition(PositionEncoding):
         super().__init__(params, ctx)
         self.head_dim = int(params["head_dim"])
         self.theta = float(params["theta"])
+        self.factor = float(params.get("scaling_factor", 1.0))
+        if not self.factor > 0.0:
+            raise ValueError(f"the rotary scaling factor must be positive, got {self.factor}")
         if self.head_dim % 2:
             raise ValueError(f"rotary positions need an even head_dim, got {self.head_dim}")
         # a request is never longer than the engine's limit nor than the model's own
         self.n_positions = min(int(params["max_positions"]), ctx.max_positions)
-        self._key = ("rope", self.head_dim, self.theta, self.n_positions)
+        self._key = ("rope", self.head_dim, self.theta, self.n_positions, self.factor)
 
     def tables(self):
         """cos and sin [positions, d/2], built on the device at first use."""
         shared = self.ctx.shared
         if self._key not in shared:
-            shared[self._key] = ops.rope_table(self.n_positions, self.head_dim, self.theta, self.ctx.device)
+            shared[self._key] = ops.rope_table(self.n_positions, self.head_dim, self.theta, self.ctx.device, self.factor)
         return shared[self._key]
 
 

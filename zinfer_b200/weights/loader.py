@@ -50,8 +50,8 @@ def check_against(path: str, available: dict[str, tuple[tuple[int, ...], torch.d
     for n, s in specs.items():
         if n in available:
             shape, dt = available[n]
-            if tuple(shape) != tuple(s.shape):
-                wrong.append(f"{n}: file has {list(shape)}, model needs {list(s.shape)}")
+            if not s.fits(shape):
+                wrong.append(f"{n}: file has {list(shape)}, model needs {list(s.shape)}{' (-1: any size)' if -1 in s.shape else ''}")
             if s.integer == dt.is_floating_point:
                 kind.append(f"{n}: file has {dt}, model needs {'an integer' if s.integer else 'a floating'} type")
     if missing or unexpected or wrong or kind:

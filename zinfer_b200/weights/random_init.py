@@ -27,6 +27,8 @@ def _seed_for(seed: int, name: str) -> int:
 def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu") -> torch.Tensor:
     gen = torch.Generator(device=device)
     gen.manual_seed(_seed_for(seed, name))
+    if -1 in spec.shape:        # free dimensions take the size the spec proposes
+        spec = TensorSpec(spec.concrete(), spec.init, spec.optional, spec.integer)
     if spec.integer:
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
     if spec.init == "norm":
