@@ -21,6 +21,8 @@ class Scaled:
 
 def add_rmsnorm(h, delta, weight, eps, out_dtype, rows=None, out=None, bias=None):
     scale = 1.0
+    if type(delta).__name__ == "Carried":      # nothing pending
+        delta = None
     if isinstance(delta, Scaled):
         delta, scale = delta.delta, delta.scale
     if rows is None:
@@ -345,7 +347,7 @@ def attention_prefill_tile_rows():
 
 
 def paged_attention(q, k_cache, v_cache, block_tables, cu_q, kv_lens, tile_seq, tile_q0, num_heads, num_kv_heads,
-                    head_dim, page_size, window, scale, out=None):
+                    head_dim, page_size, window, scale, out=None, sink=0.0):
     T = q.shape[0]
     nq, nkv, d = num_heads, num_kv_heads, head_dim
     g = nq // nkv
@@ -366,7 +368,11 @@ def paged_attention(q, k_cache, v_cache, block_tables, cu_q, kv_lens, tile_seq, 
             qt = q[t, :nq * d].to(torch.float32).reshape(nq, d)
             for h in range(nq):
                 sc = (K[:, h // g, :] @ qt[h]) * scale
-                p = torch.softmax(sc, dim=0)
+                if sink:       # `sink` keys of score 0 without a value
+                    e = torch.exp(sc - sc.max())
+                    p = e / (sink * torch.exp(-sc.max()) + e.sum())
+                else:
+                    p = torch.softmax(sc, dim=0)
                 o[t, h * d:(h + 1) * d] = p @ V[:, h // g, :]
     return o.to(q.dtype)
 
@@ -380,9 +386,9 @@ def linear_argmax(x, weight):
     return logits, argmax(logits)
 
 
-def attention(q, k_cache, v_cache, block_tables, step, num_heads, num_kv_heads, head_dim, page_size, window, scale):
+def attention(q, k_cache, v_cache, block_tables, step, num_heads, num_kv_heads, head_dim, page_size, window, scale, sink=0.0):
     return paged_attention(q, k_cache, v_cache, block_tables, step.cu_q, step.kv_lens, step.tile_seq, step.tile_q0,
-                           num_heads, num_kv_heads, head_dim, page_size, window, scale)
+                           num_heads, num_kv_heads, head_dim, page_size, window, scale, sink=sink)
 
 
 def patch_tokens(ids, prev, dst, src):
@@ -434,3 +440,153 @@ def sample(logits, temperature, seeds, draw_index, top_k=None, top_p=None, min_p
             counts[crow, tok] += 1
         res[i] = tok
     return res
+
+
+# ------------------------------------------------ the parts of the output-norm blocks and linear attention
+class Carried:
+    def __init__(self, x):
+        self.x = x
+
+
+def _plain(delta):
+    if delta is None:
+        return None
+    scale = 1.0
+    if isinstance(delta, Scaled):
+        delta, scale = delta.delta, delta.scale
+    return delta.to(torch.float32) * scale
+
+
+def norm_residual(h, a, weight, eps, out_dtype, b=None):
+    y = _plain(a)
+    if b is not None:
+        y = y + _plain(b)
+    h += y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps) * weight
+    return h if out_dtype == torch.float32 else h.to(out_dtype)
+
+
+def cast_rows(h, dtype):
+    return h if dtype == torch.float32 else h.to(dtype)
+
+
+def relu2_(x):
+    x.copy_(torch.relu(x.to(torch.float32)) ** 2)
+    return x
+
+
+def qk_prepare(qkv, num_heads, num_kv_heads, head_dim, rot_dims, q_weight, k_weight, eps, cos, sin, positions, k_cache,
+               v_cache, slots, page_size, values_from_keys=False, write_kv=True):
+    T, nq, nkv, d = qkv.shape[0], num_heads, num_kv_heads, head_dim
+    pos = positions.long()
+
+    def prep(x, w):                                        # [T, heads, d] float32
+        if w is not None:
+            x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w
+        if cos is not None:
+            x = _rotate_first(x, cos[pos][:, None, :], sin[pos][:, None, :], rot_dims)
+        return x
+
+    q = qkv[:, :nq * d].to(torch.float32).reshape(T, nq, d)
+    k_raw = qkv[:, nq * d:(nq + nkv) * d].to(torch.float32).reshape(T, nkv, d)
+    qn = prep(q, q_weight)
+    if write_kv:
+        kn = prep(k_raw, k_weight)
+        v = k_raw if values_from_keys else qkv[:, (nq + nkv) * d:(nq + 2 * nkv) * d].to(torch.float32).reshape(T, nkv, d)
+        for t in range(T):
+            slot = int(slots[t])
+            if slot < 0:
+                continue
+            k_cache[slot // page_size, :, slot % page_size] = kn[t].to(k_cache.dtype)
+            v_cache[slot // page_size, :, slot % page_size] = v[t].to(v_cache.dtype)
+    qkv[:, :nq * d] = qn.reshape(T, nq * d).to(qkv.dtype)
+    return qkv
+
+
+def _requests(step):
+    cu = [int(v) for v in step.cu_q[:step.n_seqs + 1]]
+    return [(s, cu[s], cu[s + 1], int(step.state_slots[s])) for s in range(step.n_seqs)]
+
+
+def short_conv(x, kernel, tail, step, activation="silu"):
+    T, C = x.shape
+    taps = kernel.shape[1]
+    y = torch.zeros((T, C), dtype=torch.float32)
+    for _, a, b, slot in _requests(step):
+        full = torch.cat([tail[slot].to(torch.float32).reshape(taps - 1, C), x[a:b].to(torch.float32)])
+        for t in range(b - a):
+            y[a + t] = (full[t:t + taps] * kernel.T).sum(0)
+    return y * torch.sigmoid(y) if activation == "silu" else y
+
+
+def short_conv_carry(x, taps, tail, step):
+    if taps <= 1:
+        return
+    C = x.shape[1]
+    for _, a, b, slot in _requests(step):
+        full = torch.cat([tail[slot].to(torch.float32).reshape(taps - 1, C), x[a:b].to(torch.float32)])
+        tail[slot] = full[full.shape[0] - (taps - 1):].reshape(tail[slot].shape)
+
+
+def decay_sigmoid_root_(z, bias, tau):
+    z.copy_(torch.exp(torch.nn.functional.logsigmoid(z + (bias if bias is not None else 0.0)) / tau))
+    return z
+
+
+def decay_exp_softplus_(z, bias, a_log, head_dim):
+    x = torch.nn.functional.softplus(z + (bias if bias is not None else 0.0))
+    z.copy_(torch.exp(-torch.exp(a_log).repeat_interleave(head_dim) * x))
+    return z
+
+
+def unit_norm_(x, heads, head_dim, eps, scale=1.0):
+    v = x[:, :heads * head_dim].reshape(x.shape[0], heads, head_dim)
+    x[:, :heads * head_dim] = (scale * v / torch.sqrt((v * v).sum(-1, keepdim=True) + eps)).reshape(x.shape[0], -1)
+    return x
+
+
+def sigmoid_rows(x):
+    return torch.sigmoid(x.to(torch.float32)).contiguous()
+
+
+def linear_recurrence(q, k, v, decay, beta, q_scale, state, heads, key_heads, dim, vdim, step):
+    T = q.shape[0]
+    out = torch.zeros((T, heads * vdim), dtype=torch.float32)
+    rep = heads // key_heads
+    qf, kf, vf = (t.to(torch.float32) for t in (q, k, v))
+    for _, a, b, slot in _requests(step):
+        S = state[slot].reshape(heads, dim, vdim).clone()
+        for t in range(a, b):
+            for h in range(heads):
+                kk = kf[t, (h // rep) * dim:(h // rep + 1) * dim]
+                qq = qf[t, (h // rep) * dim:(h // rep + 1) * dim] * q_scale
+                Sh = decay[t, h * dim:(h + 1) * dim].unsqueeze(-1) * S[h]
+                u = vf[t, h * vdim:(h + 1) * vdim]
+                if beta is not None:
+                    u = beta[t, h] * (u - Sh.T @ kk)
+                S[h] = Sh + kk.unsqueeze(-1) * u.unsqueeze(0)
+                out[t, h * vdim:(h + 1) * vdim] = S[h].T @ qq
+        state[slot] = S.reshape(state[slot].shape)
+    return out
+
+
+def head_norm_gate(o, weight, eps, gate, gate_kind, heads, vdim, out_dtype):
+    T = o.shape[0]
+    x = o.reshape(T, heads, vdim)
+    g = gate.to(torch.float32).reshape(T, heads, vdim)
+    act = g * torch.sigmoid(g) if gate_kind == "silu" else torch.sigmoid(g)
+    return (x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * weight * act).reshape(T, heads * vdim).to(out_dtype)
+
+
+def moe_route_grouped(logits, top, score="sigmoid", groups=1, keep=1, scale=1.0, renormalize=False):
+    T, NR = logits.shape
+    s = torch.sigmoid(logits) if score == "sigmoid" else torch.softmax(logits, dim=-1)
+    per = NR // groups
+    gscore = s.reshape(T, groups, per).topk(min(2, per), dim=-1).values.sum(-1)
+    best = gscore.topk(keep, dim=-1).indices
+    allowed = torch.zeros((T, groups), dtype=torch.bool).scatter_(1, best, True).repeat_interleave(per, dim=1)
+    pick = torch.where(allowed, s, torch.full_like(s, -float("inf")))
+    chosen = pick.topk(top, dim=-1).indices
+    weight = s.gather(1, chosen)
+    if renormalize:
+        weight = weight / weight.sum(-1, keepdim=True)
+    return chosen.to(torch.int32), (weight * scale).to(torch.float32)

@@ -15,6 +15,7 @@ import math
 import torch
 
 F64 = torch.float64
+SINK = 1.0      # the attention's softmax counts this much beside the keys' exponentials (a test sets 0 to show it matters)
 
 
 def _w(t):
@@ -84,7 +85,7 @@ def sink_attention(h, p, m, eps, pos0=0, cache=None):
             g = hd // (H // G)
             s = (keys[:n, g] @ qn[t, hd]) * float(m["scale"])
             e = torch.exp(s)
-            w = e / (1.0 + e.sum())                 # the sink: score 0, no value
+            w = e / (SINK + e.sum())                # the sink: score 0, no value
             out[t, hd] = w @ vals[:n, g]
     return out.reshape(T, H * D) @ _w(p["o"]).T, (keys, vals)
 

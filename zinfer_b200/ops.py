@@ -1193,6 +1193,8 @@ def relu2_(x: torch.Tensor) -> torch.Tensor:
 # ------------------------------------------- mixers with a matrix-valued state per head
 def _slot_view(state: torch.Tensor, name: str):
     """(tensor, elements from one slot to the next) of a float32 per-request state that may be a view of wider rows."""
+    if state.numel() == 0:
+        return state, 0
     _need(state.dtype == torch.float32 and state.dim() >= 2 and all(
         state.stride(i) == state.stride(i + 1) * state.shape[i + 1] for i in range(1, state.dim() - 1)) and state.stride(-1) == 1,
         f"{name}: a float32 state whose slots are dense")
