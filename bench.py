@@ -22,7 +22,8 @@ for every request).  Prints ONE JSON line:
 With ``--design luvavik`` it runs another measurement instead and prints a JSON line of its own: prefill
 (2,048 tokens) and decode (batch 8, 2,048 cached tokens each) throughput of the Luvavik design at layer
 sizes of real models (widths 2048 and 4096; ``--design-sizes``), beside Qwen3 dense at the same width,
-layer count and multiply-adds per token; ``--profile PATH`` adds both models' per-kernel-class times and
+layer count and multiply-adds per token; ``--design rogosun`` does the same for the Rogosun design, beside
+Luvavik (the nearest design the engine has) and Qwen3; ``--profile PATH`` adds both models' per-kernel-class times and
 roofline fractions.  The default workload and its output line are untouched.
 
 Peaks come from MEASURED_PEAKS.json when the driver wrote it, else the fallback
@@ -140,6 +141,28 @@ def luvavik_shape(width: int, heads: int, experts: int, top: int, expert_ff: int
             "max_position_embeddings": 8192}
 
 
+def rogosun_shape(width: int, heads: int, experts: int, top: int, expert_ff: int, dense_ff: int) -> dict:
+    """A Rogosun configuration with layers the size of a real model's: gated linear attention with key heads of 128
+    and value heads of 256 channels (keys half as wide as the model, values as wide), parallel layers of attention
+    (heads of 128 of which 64 dimensions rotate, four query heads per kv head, a sink, the raw keys as values) beside
+    a gated delta rule (heads of 128 x 256 behind convolutions of four taps), dense feed-forwards and routed experts
+    in groups of four with a shared expert.  Seven layers."""
+    g = max(1, width // 256)
+    gla = {"type": "gla", "mixer": {"heads": g, "dim": 128, "vdim": 256, "tau": 16.0}}
+    par = {"type": "parallel", "mixer": {
+        "left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 4.0}}},
+        "right": {"heads": g, "kv_heads": max(1, g // 2), "dim": 128, "vdim": 256, "conv": 4},
+        "left_scale": 0.8, "right_scale": 0.5}}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": expert_ff},
+           "router": {"experts": experts, "top": top, "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
+    dense = {"kind": "dense", "ff": dense_ff}
+    layers = [dict(gla, mlp=dense), dict(par, mlp=moe), dict(gla, mlp=moe), dict(gla, mlp=moe), dict(par, mlp=dense),
+              dict(gla, mlp=moe), dict(par, mlp=moe)]
+    return {"architecture": "Rogosun", "vocab": 32768, "width": width, "layers": layers, "norm": {"eps": 1e-6},
+            "max_position_embeddings": 8192}
+
+
 DESIGN_SIZES = {
     # name: (width, heads, experts, chosen, expert ff, dense ff); Qwen3 beside it: the same width, layer runs and
     # heads of 128, a feed-forward as wide as the chosen experts together (equal products per token)
@@ -219,6 +242,11 @@ def compare_designs(args) -> int:
     for size in (args.design_sizes.split(",") if args.design_sizes else DESIGN_SIZES):
         width, heads, experts, top, eff, dff = DESIGN_SIZES[size]
         raw = luvavik_shape(width, heads, experts, top, eff, dff)
+        if args.design == "rogosun":
+            # beside Luvavik, the nearest design the engine has (recurrent layers, attention, routed experts), and Qwen3
+            from zinfer_b200.config import RogosunConfig
+            own = rogosun_shape(width, heads, experts, top, eff, dff)
+            results[f"rogosun_{size}"] = measure(f"rogosun_{size}", RogosunConfig.from_dict(own), own["vocab"])
         results[f"luvavik_{size}"] = measure(f"luvavik_{size}", LuvavikConfig.from_dict(raw), raw["vocab"])
         # two products of an expert against three of the gated feed-forward: equal multiply-adds per token
         qwen = dict(QWEN3_8B, vocab_size=raw["vocab"], hidden_size=width, intermediate_size=(2 * top * eff) // 3 // 64 * 64,
@@ -228,7 +256,8 @@ def compare_designs(args) -> int:
     if args.profile:
         with open(args.profile, "w") as f:
             json.dump(profiles, f, indent=1)
-    print(json.dumps({"metric": "prefill and decode tokens/s, Luvavik beside Qwen3 dense at equal width and layer runs",
+    names = "Rogosun beside Luvavik and Qwen3 dense" if args.design == "rogosun" else "Luvavik beside Qwen3 dense"
+    print(json.dumps({"metric": f"prefill and decode tokens/s, {names} at equal width and layer runs",
                       "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16",
                       "data": "synthetic", "config": {"prefill_tokens": tokens, "decode_batch": batch, "context": context,
                                                       "layer_runs": 7, "peaks": peak_src}, "results": results}))
@@ -251,7 +280,7 @@ def main() -> int:
                     help="with ZINFER_B200_TRACE=1 in the environment: write the timeline of one decode step at the "
                          "headline batch (every kernel's start, the completion of what it depends on, and what it adds "
                          "to the chain) there as JSON, and do nothing else")
-    ap.add_argument("--design", default=None, choices=["luvavik"],
+    ap.add_argument("--design", default=None, choices=["luvavik", "rogosun"],
                     help="instead of the default benchmark: prefill and decode throughput of this design at layer sizes "
                          "of real models beside Qwen3 dense at equal size (a JSON line of its own)")
     ap.add_argument("--design-sizes", default=None, help="with --design: widths to run, e.g. 2048 or 2048,4096")

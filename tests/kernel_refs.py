@@ -590,3 +590,7 @@ def moe_route_grouped(logits, top, score="sigmoid", groups=1, keep=1, scale=1.0,
     if renormalize:
         weight = weight / weight.sum(-1, keepdim=True)
     return chosen.to(torch.int32), (weight * scale).to(torch.float32)
+
+
+def moe_router_grouped(x, w_router, top, score="sigmoid", groups=1, keep=1, scale=1.0, renormalize=False):
+    return moe_route_grouped(x.to(torch.float32) @ w_router.to(torch.float32).T, top, score, groups, keep, scale, renormalize)

@@ -433,6 +433,41 @@ def test_decode_attention_both_tile_forms(nq, nkv, d, page, window):
     o.require_kernel_status_ok("decode attention")
 
 
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(6, 1, 64, 16, None), (32, 8, 128, 16, None), (6, 1, 64, 8, 37),
+                                                   (2, 1, 256, 16, None), (5, 5, 64, 16, 200), (24, 2, 128, 32, None)])
+def test_attention_with_a_sink_on_the_tensor_cores(nq, nkv, d, page, window):
+    """A softmax whose denominator counts a sink (keys of score 0 without a value), by the tensor-core kernels whose
+    weights meet the values as two bfloat16 parts: single tokens (both tile forms, TMA and cp.async, with and without
+    key splits) and prompt portions, against the reference and against the exact kernel.  Scores are kept small so
+    that the sink holds a large share of every denominator."""
+    o = ops()
+    for q_lens, ctx_lens in (([1] * 8, [0, 15, 16, 63, 64, 65, 700, 1300]), ([1, 130, 17, 1, 300], [5, 0, 250, 1000, 40])):
+        args = _paged_case(torch.bfloat16, nq, nkv, d, page, q_lens, ctx_lens, seed=16)
+        step = _as_step(args, q_lens, ctx_lens)
+        scale = float(0.3 / np.sqrt(d))
+        want = ref.paged_attention(window=window, scale=scale, sink=1.5, **args).float()
+        plain = ref.paged_attention(window=window, scale=scale, **args).float()
+        assert (want - plain).abs().max() > 0.05 * plain.abs().max()                 # the sink matters
+        exact = o.paged_attention(window=window, scale=scale, sink=1.5, **args).float()
+        torch.testing.assert_close(exact, want, rtol=1.6e-2, atol=1.5e-2)
+        if d == 256 and max(q_lens) > 1:
+            continue                                  # prompt portions of heads of 256 go to the exact kernel
+        try:
+            for tma in (True, False):
+                o.decode_tma(tma)
+                for on in (True, False):
+                    o.decode_transposed_tile(on)
+                    for forced in (1, 5):
+                        step.max_kv_len = 64 * forced
+                        got = o.attention(args["q"], args["k_cache"], args["v_cache"], args["block_tables"], step, nq, nkv, d,
+                                          page, window, scale, sink=1.5).float()
+                        torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1.5e-2)
+        finally:
+            o.decode_transposed_tile(True)
+            o.decode_tma(1)
+    o.require_kernel_status_ok("attention with a sink")
+
+
 @pytest.mark.parametrize("nq,nkv,d,page,window,norm,rope,partial", [
     (32, 8, 128, 16, None, True, True, True), (8, 2, 128, 16, None, True, True, False), (6, 1, 64, 8, 50, True, True, False),
     (5, 5, 64, 32, None, False, True, False), (16, 1, 128, 16, None, True, False, False), (2, 1, 256, 16, None, True, True, False)])

@@ -144,6 +144,9 @@ int zi_linear_recurrence(float* out, int ldo, const void* q, int ldq, const void
                          const int* state_slots, int n_seqs, cudaStream_t stream);
 int zi_head_norm_gate(void* out, int out_dtype, int ldo, const float* o, int ldi, const float* w, float eps,
                       const void* gate, int gate_dtype, int ldgate, int act, int T, int heads, int V, cudaStream_t stream);
+int zi_moe_router_grouped(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w, int w_dtype, int T,
+                          int K, int NR, int top, int renormalize, int score_kind, int groups, int keep, float wscale,
+                          cudaStream_t stream);
 int zi_moe_route_grouped(int* chosen, float* weight, const float* logits, int T, int NR, int top, int renormalize,
                          int score_kind, int groups, int keep, float wscale, cudaStream_t stream);
 // Latent attention: the cached row [normed latent | rotated key part] and the rotated query part of a token.
@@ -190,6 +193,16 @@ int zi_attention_prefill_tcgen05(void* out, int out_stride, const void* q, int q
                                  int bt_stride, const int* cu_q, const int* kv_lens, const int* tile_seq,
                                  const int* tile_q0, int n_tiles, int nq, int nkv, int d, int page_size, int window,
                                  float scale, cudaStream_t stream);
+// Both with the softmax weights as two bfloat16 parts where they meet the values, and a sink in the denominator.
+int zi_attention_prefill_mma_sink(void* out, int out_stride, const void* q, int q_stride, const void* kcache,
+                                  const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
+                                  const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
+                                  int d, int page_size, int window, float scale, float sink, cudaStream_t stream);
+int zi_attention_decode_mma_sink(void* out, int out_stride, float* workspace, const void* q, int q_stride,
+                                 const void* kcache, const void* vcache, long long n_pages, const int* block_tables,
+                                 int bt_stride, const int* cu_q, const int* kv_lens, const int* dec_seq, int n_dec, int nq,
+                                 int nkv, int d, int page_size, int window, float scale, int splits, float sink,
+                                 cudaStream_t stream);
 long long zi_attention_decode_workspace_floats(int n_dec, int nq, int nkv, int d, int splits);
 int zi_attention_decode_mma(void* out, int out_stride, float* workspace, const void* q, int q_stride,
                             const void* kcache, const void* vcache, long long n_pages, const int* block_tables, int bt_stride,

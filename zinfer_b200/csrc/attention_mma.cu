@@ -27,14 +27,16 @@ namespace {
 // =============================================================================== prefill
 constexpr int PF_BQ = 128, PF_BK = 64, PF_THREADS = 256;
 
-template <int D>
+// XP: the softmax weights meet the values as two bfloat16 parts (high and rest: 16 bits of mantissa), and `sink`
+// keys of score 0 without a value count in the denominator.
+template <int D, bool XP>
 __global__ void __launch_bounds__(PF_THREADS, 2)
 attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restrict__ q, int q_stride,
                         const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                         const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_q,
                         const int* __restrict__ kv_lens, const int* __restrict__ tile_seq,
                         const int* __restrict__ tile_q0, int nq, int nkv, int page_size, int page_shift,
-                        int window, float scale_log2) {
+                        int window, float scale_log2, float sink) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(128) uint8_t smem[];
@@ -160,6 +162,11 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
         uint32_t pf[4] = {pack_bf16(s[2 * kp][0], s[2 * kp][1]), pack_bf16(s[2 * kp][2], s[2 * kp][3]),
                           pack_bf16(s[2 * kp + 1][0], s[2 * kp + 1][1]), pack_bf16(s[2 * kp + 1][2], s[2 * kp + 1][3])};
         pv_16keys<D>(o, pf, vs_addr, kp * 16, lane);
+        if constexpr (XP) {
+          uint32_t pr[4] = {pack_bf16_rest(s[2 * kp][0], s[2 * kp][1]), pack_bf16_rest(s[2 * kp][2], s[2 * kp][3]),
+                            pack_bf16_rest(s[2 * kp + 1][0], s[2 * kp + 1][1]), pack_bf16_rest(s[2 * kp + 1][2], s[2 * kp + 1][3])};
+          pv_16keys<D>(o, pr, vs_addr, kp * 16, lane);
+        }
       }
     }
     __syncthreads();  // the other buffer is refilled in the next iteration
@@ -172,6 +179,7 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     const int r = row_lo + i * 8;
     if (r < nqv) {
+      if (XP && sink > 0.f) sum += sink * exp2f(-m[i]);      // the sink's score is 0
       const float inv = 1.0f / sum;
       bf16* orow = out + (size_t)(tok0 + q0 + r) * out_stride + (size_t)h * D + 2 * (lane & 3);
 #pragma unroll
@@ -186,7 +194,7 @@ struct BlockSync {
   static __device__ __forceinline__ void sync() { __syncthreads(); }
 };
 
-template <int D, bool FUSED, bool TR, bool TMA>
+template <int D, bool FUSED, bool TR, bool TMA, bool XP = false>
 __global__ void __launch_bounds__(DC_THREADS)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        int* __restrict__ status, bf16* __restrict__ out, int out_stride, float* __restrict__ partial,
@@ -194,7 +202,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        const bf16* __restrict__ vcache, const int* __restrict__ block_tables, int bt_stride,
                        const int* __restrict__ cu_q, const int* __restrict__ kv_lens,
                        const int* __restrict__ dec_seq, int nq, int nkv, int page_size, int page_shift, int window,
-                       float scale_log2, int splits, const FusedQK fq) {
+                       float scale_log2, int splits, const FusedQK fq, float sink) {
   pdl_launch_dependents();
   // (the unit waits for the kernel before this one itself, after it has asked for its first keys)
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -203,23 +211,23 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   constexpr int RING_BYTES = DC_WARPS * DecodeCfg<D>::STAGES * 2 * DC_KEYS * D * 2;
   constexpr int FUSED_BYTES = FUSED ? 16 * D * 2 + (2 * D + 16) * (int)sizeof(float) : 0;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + RING_BYTES + ((FUSED_BYTES + 15) & ~15));
-  attn_decode_unit<D, FUSED, BlockSync, DecodeCfg<D>::STAGES, TR, TMA>(
+  attn_decode_unit<D, FUSED, BlockSync, DecodeCfg<D>::STAGES, TR, TMA, XP>(
       smem, threadIdx.x, blockIdx.x, blockIdx.y, blockIdx.z, out, out_stride, partial, q, q_stride, kcache, vcache,
       block_tables, bt_stride, cu_q, kv_lens, dec_seq, nq, nkv, page_size, page_shift, window, scale_log2, splits, fq,
-      nullptr, &map_k, &map_v, bars, status);
+      nullptr, &map_k, &map_v, bars, status, sink);
 }
 
 template <int D>
 __global__ void attn_decode_combine_kernel(bf16* __restrict__ out, int out_stride, const float* __restrict__ partial,
                                            const int* __restrict__ cu_q, const int* __restrict__ dec_seq, int nq,
-                                           int nkv, int splits) {
+                                           int nkv, int splits, float sink) {
   pdl_launch_dependents();
   // which token this is comes from the step's own arrays (copied before any kernel of the step):
   // these two dependent loads need not wait for the attention kernel
   const int token = cu_q[dec_seq[blockIdx.x]];
   pdl_wait();
   attn_decode_combine_item<D>(blockIdx.x, blockIdx.y, threadIdx.x, blockDim.x, out, out_stride, partial, token, nq, nkv,
-                              splits);
+                              splits, sink);
 }
 
 
@@ -227,15 +235,15 @@ template <int D>
 int launch_prefill(void* out, int out_stride, const void* q, int q_stride, const void* kc, const void* vc,
                    const int* bt, int bt_stride, const int* cu_q, const int* kv_lens, const int* tile_seq,
                    const int* tile_q0, int n_tiles, int nq, int nkv, int page_size, int window, float scale,
-                   cudaStream_t stream) {
-  auto kern = attn_prefill_mma_kernel<D>;
+                   cudaStream_t stream, bool xp = false, float sink = 0.f) {
+  auto kern = xp ? attn_prefill_mma_kernel<D, true> : attn_prefill_mma_kernel<D, false>;
   const size_t smem = (size_t)(PF_BQ + 4 * PF_BK) * D * 2;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return zi_refuse("attention_prefill: cannot get %zu bytes of shared memory", smem);
   dim3 grid(nq, n_tiles);
   zi_launch(kern, dim3(grid), dim3(PF_THREADS), smem, stream, (bf16*)out, out_stride, (const bf16*)q, q_stride, (const bf16*)kc,
                                            (const bf16*)vc, bt, bt_stride, cu_q, kv_lens, tile_seq, tile_q0, nq, nkv,
-                                           page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f);
+                                           page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f, sink);
   return zi_check_launch("attention_prefill");
 }
 
@@ -243,12 +251,12 @@ int g_decode_transposed = 1;   // zi_attention_decode_transposed(0) switches the
 
 int g_decode_tma = 1;          // see zi_attention_decode_tma
 
-template <int D, bool FUSED, bool TR, bool TMA>
+template <int D, bool FUSED, bool TR, bool TMA, bool XP = false>
 int launch_decode_as(void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
                      const void* vc, long long n_pages, const int* bt, int bt_stride, const int* cu_q,
                      const int* kv_lens, const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window,
-                     float scale, int splits, const FusedQK& fq, cudaStream_t stream) {
-  auto kern = attn_decode_mma_kernel<D, FUSED, TR, TMA>;
+                     float scale, int splits, const FusedQK& fq, cudaStream_t stream, float sink = 0.f) {
+  auto kern = attn_decode_mma_kernel<D, FUSED, TR, TMA, XP>;
   CUtensorMap map_k, map_v;
   memset(&map_k, 0, sizeof(map_k));
   memset(&map_v, 0, sizeof(map_v));
@@ -269,7 +277,7 @@ int launch_decode_as(void* out, int out_stride, float* partial, const void* q, i
   dim3 grid(n_dec, nkv, splits);
   zi_launch(kern, dim3(grid), dim3(DC_THREADS), smem, stream, map_k, map_v, status, (bf16*)out, out_stride,
             splits > 1 ? partial : nullptr, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, bt, bt_stride, cu_q,
-            kv_lens, dec_seq, nq, nkv, page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f, splits, fq);
+            kv_lens, dec_seq, nq, nkv, page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f, splits, fq, sink);
   return 0;
 }
 
@@ -277,7 +285,7 @@ template <int D, bool FUSED>
 int launch_decode(void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
                   const void* vc, long long n_pages, const int* bt, int bt_stride, const int* cu_q, const int* kv_lens,
                   const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window, float scale, int splits,
-                  const FusedQK& fq, cudaStream_t stream) {
+                  const FusedQK& fq, cudaStream_t stream, bool xp = false, float sink = 0.f) {
   // Groups of at most 8 query heads take the transposed tile (keys on the MMA's rows).  Keys and values come by
   // TMA (page boxes, pages of 8, 16, 32, ... tokens whose rows a tensor map can address) while the requests
   // are few, and by cp.async from every lane when they are many.  Measured per 36-layer step (Qwen3-8B
@@ -291,15 +299,26 @@ int launch_decode(void* out, int out_stride, float* partial, const void* q, int 
 #define ZI_DECODE_AS(TR_, TMA_)                                                                                        \
   launch_decode_as<D, FUSED, TR_, TMA_>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q, kv_lens, \
                                         dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream)
-  int rc0 = tr ? (tma ? ZI_DECODE_AS(true, true) : ZI_DECODE_AS(true, false))
-               : (tma ? ZI_DECODE_AS(false, true) : ZI_DECODE_AS(false, false));
+#define ZI_DECODE_XP(TR_, TMA_)                                                                                        \
+  launch_decode_as<D, false, TR_, TMA_, true>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q,    \
+                                              kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, sink)
+  int rc0;
+  if constexpr (!FUSED) {
+    if (xp)     // exact weights and a sink: the kernel that only reads q (the fused form makes whole-head rotations)
+      rc0 = tr ? (tma ? ZI_DECODE_XP(true, true) : ZI_DECODE_XP(true, false)) : (tma ? ZI_DECODE_XP(false, true) : ZI_DECODE_XP(false, false));
+    else
+      rc0 = tr ? (tma ? ZI_DECODE_AS(true, true) : ZI_DECODE_AS(true, false)) : (tma ? ZI_DECODE_AS(false, true) : ZI_DECODE_AS(false, false));
+  } else {
+    rc0 = tr ? (tma ? ZI_DECODE_AS(true, true) : ZI_DECODE_AS(true, false)) : (tma ? ZI_DECODE_AS(false, true) : ZI_DECODE_AS(false, false));
+  }
+#undef ZI_DECODE_XP
 #undef ZI_DECODE_AS
   if (rc0) return rc0;
   int rc = zi_check_launch("attention_decode");
   if (rc) return rc;
   if (splits > 1) {
     zi_launch(attn_decode_combine_kernel<D>, dim3(n_dec, nq), dim3(D >= 128 ? 128 : 64), 0, stream, (bf16*)out,
-              out_stride, partial, cu_q, dec_seq, nq, nkv, splits);
+              out_stride, partial, cu_q, dec_seq, nq, nkv, splits, sink);
     rc = zi_check_launch("attention_decode_combine");
   }
   return rc;
@@ -309,15 +328,15 @@ template <bool FUSED>
 int dispatch_decode(int d, void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
                     const void* vc, long long n_pages, const int* bt, int bt_stride, const int* cu_q, const int* kv_lens,
                     const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window, float scale, int splits,
-                    const FusedQK& fq, cudaStream_t stream) {
+                    const FusedQK& fq, cudaStream_t stream, bool xp = false, float sink = 0.f) {
   if (d == 64)
     return launch_decode<64, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q, kv_lens, dec_seq,
-                                    n_dec, nq, nkv, page_size, window, scale, splits, fq, stream);
+                                    n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, xp, sink);
   if (d == 128)
     return launch_decode<128, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q, kv_lens,
-                                     dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream);
+                                     dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, xp, sink);
   return launch_decode<256, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q, kv_lens, dec_seq,
-                                   n_dec, nq, nkv, page_size, window, scale, splits, fq, stream);
+                                   n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, xp, sink);
 }
 }  // namespace
 
@@ -359,6 +378,40 @@ extern "C" int zi_attention_prefill_mma(void* out, int out_stride, const void* q
                               tile_seq, tile_q0, n_tiles, nq, nkv, page_size, window, scale, stream);
   return launch_prefill<128>(out, out_stride, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
                              tile_seq, tile_q0, n_tiles, nq, nkv, page_size, window, scale, stream);
+}
+
+// The same with the softmax weights as two bfloat16 parts (16 bits of mantissa where they meet the values) and
+// `sink` keys of score 0 without a value in the denominator.
+extern "C" int zi_attention_prefill_mma_sink(void* out, int out_stride, const void* q, int q_stride, const void* kcache,
+                                             const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
+                                             const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles,
+                                             int nq, int nkv, int d, int page_size, int window, float scale, float sink,
+                                             cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (!zi_attention_mma_supported(nq, nkv, d, 0)) return zi_refuse("attention_prefill: head_dim %d is not 64 or 128", d);
+  if (q_stride % 8 || ((uintptr_t)q % 16)) return zi_refuse("attention_prefill: q rows must be 16-byte aligned");
+  if (!(sink >= 0.f)) return zi_refuse("attention_prefill: the sink's weight must not be negative");
+  if (d == 64)
+    return launch_prefill<64>(out, out_stride, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
+                              tile_seq, tile_q0, n_tiles, nq, nkv, page_size, window, scale, stream, true, sink);
+  return launch_prefill<128>(out, out_stride, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
+                             tile_seq, tile_q0, n_tiles, nq, nkv, page_size, window, scale, stream, true, sink);
+}
+
+extern "C" int zi_attention_decode_mma_sink(void* out, int out_stride, float* workspace, const void* q, int q_stride,
+                                            const void* kcache, const void* vcache, long long n_pages,
+                                            const int* block_tables, int bt_stride, const int* cu_q, const int* kv_lens,
+                                            const int* dec_seq, int n_dec, int nq, int nkv, int d, int page_size,
+                                            int window, float scale, int splits, float sink, cudaStream_t stream) {
+  if (n_dec <= 0) return 0;
+  if (!zi_attention_mma_supported(nq, nkv, d, 1))
+    return zi_refuse("attention_decode: head_dim %d (64, 128, 256) or group size %d (<= 16) is not supported", d, nq / nkv);
+  if (splits < 1 || (splits > 1 && !workspace)) return zi_refuse("attention_decode: %d splits need a workspace", splits);
+  if (q_stride % 2) return zi_refuse("attention_decode: q rows must be 4-byte aligned");
+  if (!(sink >= 0.f)) return zi_refuse("attention_decode: the sink's weight must not be negative");
+  FusedQK none = {};
+  return dispatch_decode<false>(d, out, out_stride, workspace, q, q_stride, kcache, vcache, n_pages, block_tables, bt_stride, cu_q,
+                                kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, none, stream, true, sink);
 }
 
 // Floats of workspace a decode launch with `splits` > 1 needs.

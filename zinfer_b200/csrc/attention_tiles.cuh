@@ -41,6 +41,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// What bfloat16 drops of two softmax weights: p - bf16(p), packed.  The weights' product with the values then runs
+// twice, over the high and the low parts, and the weights count with 16 bits of mantissa instead of 8.
+__device__ __forceinline__ uint32_t pack_bf16_rest(float lo, float hi) {
+  const float rl = lo - __bfloat162float(__float2bfloat16_rn(lo)), rh = hi - __bfloat162float(__float2bfloat16_rn(hi));
+  return pack_bf16(rl, rh);
+}
+
 // Byte offset of 16-byte chunk `c` of row `r` in a swizzled [rows][D] bf16 tile.
 template <int D> __device__ __forceinline__ uint32_t swz(int r, int c) {
   return (uint32_t)(r * D * 2 + ((c ^ (r & 7)) << 4));
@@ -339,7 +346,9 @@ struct FusedQK {
 // one lane issuing, completion on a barrier per warp and stage (`bars`, DC_WARPS * STAGES of them, which
 // the caller places in shared memory; `smem` is then 1024-byte aligned) with a bounded wait that records
 // a code in `status`; else by cp.async from every lane.
-template <int D, bool FUSED, class Sync, int STAGES = DecodeCfg<D>::STAGES, bool TR = false, bool TMA = false>
+// XP: the softmax weights meet the values as two bfloat16 parts (high and rest), and `sink` keys of score 0
+// without a value count in the denominator (where the unit itself divides; else the kernel that combines the splits does).
+template <int D, bool FUSED, class Sync, int STAGES = DecodeCfg<D>::STAGES, bool TR = false, bool TMA = false, bool XP = false>
 __device__ __forceinline__ void attn_decode_unit(
     uint8_t* smem, int tid, int dec, int kvh, int z, bf16* __restrict__ out, int out_stride,
     float* __restrict__ partial, const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kcache,
@@ -347,7 +356,7 @@ __device__ __forceinline__ void attn_decode_unit(
     const int* __restrict__ cu_q, const int* __restrict__ kv_lens, const int* __restrict__ dec_seq, int nq, int nkv,
     int page_size, int page_shift, int window, float scale_log2, int splits, const FusedQK& fq,
     uint8_t* fused_area = nullptr, const CUtensorMap* map_k = nullptr, const CUtensorMap* map_v = nullptr,
-    uint64_t* bars = nullptr, int* status = nullptr) {
+    uint64_t* bars = nullptr, int* status = nullptr, float sink = 0.f) {
 
   constexpr int ROWS_BYTES = DC_KEYS * D * 2;                  // one warp's 16 keys of K (or V)
   constexpr int WARP_BYTES = STAGES * 2 * ROWS_BYTES;          // a warp's private ring
@@ -412,7 +421,7 @@ __device__ __forceinline__ void attn_decode_unit(
   };
   // Not fused: the kernel before this one wrote the newest token's key and value (and q).  The first
   // tiles are asked for before the wait for it unless they may hold that key.
-  const bool early = !FUSED && kt0 + (t_begin + STAGES - 1) * DC_TILE <= pos;
+  const bool early = !FUSED && !XP && kt0 + (t_begin + STAGES - 1) * DC_TILE <= pos;
   if (!FUSED && !early) pdl_wait();
   int pg_next = lookup(0);
 #pragma unroll
@@ -676,6 +685,11 @@ __device__ __forceinline__ void attn_decode_unit(
         const uint32_t pb0 = movmatrix_trans(pack_bf16(st[0], st[1]));   // keys 0..7 of the tile
         const uint32_t pb1 = movmatrix_trans(pack_bf16(st[2], st[3]));   // keys 8..15
         pv_16keys_t<D, TMA>(ot, pb0, pb1, vs_addr, lane);
+        if constexpr (XP) {
+          const uint32_t rb0 = movmatrix_trans(pack_bf16_rest(st[0], st[1]));
+          const uint32_t rb1 = movmatrix_trans(pack_bf16_rest(st[2], st[3]));
+          pv_16keys_t<D, TMA>(ot, rb0, rb1, vs_addr, lane);
+        }
       } else {
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       qk_16keys<D, TMA>(s, qf, ks_addr, 0, lane);
@@ -694,6 +708,11 @@ __device__ __forceinline__ void attn_decode_unit(
       uint32_t pf[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]),
                         pack_bf16(s[1][2], s[1][3])};
       pv_16keys<D, TMA>(o, pf, vs_addr, 0, lane);
+      if constexpr (XP) {
+        uint32_t pr[4] = {pack_bf16_rest(s[0][0], s[0][1]), pack_bf16_rest(s[0][2], s[0][3]), pack_bf16_rest(s[1][0], s[1][1]),
+                          pack_bf16_rest(s[1][2], s[1][3])};
+        pv_16keys<D, TMA>(o, pr, vs_addr, 0, lane);
+      }
       }
     }
     __syncwarp();  // the stage is refilled by this warp's next issue
@@ -775,6 +794,7 @@ __device__ __forceinline__ void attn_decode_unit(
         dst[D + 1] = lt;
       }
     } else {
+      if (XP && sink > 0.f) lt += sink * exp2f(-mt);      // the sink's score is 0
       out[(size_t)token * out_stride + (size_t)(kvh * g + r) * D + c] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
     }
   }
@@ -785,7 +805,7 @@ __device__ __forceinline__ void attn_decode_unit(
 template <int D>
 __device__ __forceinline__ void attn_decode_combine_item(int dec, int h, int tid, int nthreads, bf16* __restrict__ out,
                                                          int out_stride, const float* partial, int token, int nq,
-                                                         int nkv, int splits) {
+                                                         int nkv, int splits, float sink = 0.f) {
   const int g = nq / nkv, kvh = h / g, r = h % g;
   const float* base = partial + ((((size_t)dec * nkv + kvh) * splits) * g + r) * (D + 2);
   const size_t zstride = (size_t)g * (D + 2);
@@ -801,6 +821,7 @@ __device__ __forceinline__ void attn_decode_combine_item(int dec, int h, int tid
     const float sc = mz == -INFINITY ? 0.f : exp2f(mz - mt);
     float lt = 0.f;
     for (int z = 0; z < splits; ++z) lt += __shfl_sync(0xffffffffu, lz * sc, z);   // in split order
+    if (sink > 0.f) lt += sink * exp2f(-mt);      // a sink: keys of score 0 without a value, in the denominator only
     for (int c = tid; c < D; c += nthreads) {   // whole warps run this loop together (D is a multiple of nthreads or the reverse)
       float acc = 0.f;
       for (int z0 = 0; z0 < splits; z0 += 8) {
@@ -824,6 +845,7 @@ __device__ __forceinline__ void attn_decode_combine_item(int dec, int h, int tid
       acc += base[z * zstride + c] * sc;
       lt += base[z * zstride + D + 1] * sc;
     }
+    if (sink > 0.f) lt += sink * exp2f(-mt);
     out[(size_t)token * out_stride + (size_t)h * D + c] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
   }
 }

@@ -9,7 +9,7 @@
 //     S <- S + k_t u_t^T ;  o_t = S^T (q_scale q_t)
 // Everything here is 32-bit arithmetic.  A request's tokens of this step are rows cu_q[s] ..
 // cu_q[s+1]-1 of the flat batch and continue the request from slot state_slots[s].  Each column of S
-// is visited by one group of threads, token after token, in an order that depends on D alone, so a
+// is visited by one group of lanes, token after token, in an order that depends on D alone, so a
 // result depends neither on how the request was cut into steps nor on the batch.
 #include "api.h"
 #include "common.cuh"
@@ -116,13 +116,15 @@ __global__ void sigmoid_rows_kernel(float* __restrict__ out, int ldo, const T* _
 }
 
 // --------------------------------------------------------------------------- the recurrence
-// Block: one request, one head, VB = 32 neighbouring value channels.  Thread (p, j) keeps R rows
-// p*R .. p*R+R-1 of column j of S in registers; the sums over a column's rows meet through shared
-// memory in the order p = 0, 1, ...  Tokens are staged TB at a time.
-constexpr int VB = 32, TB = 8;
+// Block: one request, one head, CB neighbouring value channels; 8 warps.  A column of S (D key channels of one
+// value channel) belongs to P neighbouring lanes of one warp, R = 8 (or 16) rows each, in registers; the sums over
+// a column's rows meet by a butterfly of shuffles over those P lanes (a fixed order), so nothing in the loop over
+// tokens waits for another warp.  q, k and the decays of TB tokens at a time are staged in shared memory for the
+// whole block, the next TB tokens being fetched while these are worked on (one barrier per TB tokens).
+constexpr int LR_WARPS = 8, LR_THREADS = LR_WARPS * 32, TB = 16;
 
 template <typename TQ, typename TV, int R, bool DELTA>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(LR_THREADS)
 linear_recurrence_kernel(float* __restrict__ out, int ldo, const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k,
                          int ldk, const TV* __restrict__ v, int ldv, const float* __restrict__ decay, int ldg,
                          const float* __restrict__ beta, int ldb, float q_scale, float* __restrict__ state,
@@ -130,18 +132,14 @@ linear_recurrence_kernel(float* __restrict__ out, int ldo, const TQ* __restrict_
                          const int* __restrict__ state_slots) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   const int DP = P * R;                      // key channels rounded up to whole parts
-  float* qs = sm;                            // [TB][DP]
-  float* ks = qs + TB * DP;                  // [TB][DP]
-  float* gs = ks + TB * DP;                  // [TB][DP]
-  float* vs = gs + TB * DP;                  // [TB][VB]
-  float* kq = vs + TB * VB;                  // [TB]
-  float* bs = kq + TB;                       // [TB]
-  float* red = bs + TB;                      // [2 parities][2 sums][P][VB]
-  const int s = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * VB;
-  const int tid = threadIdx.x, nthreads = blockDim.x;
-  const int p = tid / VB, j = tid % VB, col = j0 + j;
+  const int CW = 32 / P, CB = LR_WARPS * CW; // columns per warp and per block
+  const int BUF = 3 * TB * DP + TB * CB + TB;   // one staging buffer: q, k, g [TB][DP], v [TB][CB], beta [TB]
+  const int s = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * CB;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int p = lane % P, cw = lane / P;
+  const int cb = warp * CW + cw, col = j0 + cb;     // column within the block, and of the head
   const int kvh = h / (H / G);
   const int tok0 = cu_q[s], qlen = cu_q[s + 1] - tok0;
   if (qlen <= 0) return;
@@ -152,60 +150,64 @@ linear_recurrence_kernel(float* __restrict__ out, int ldo, const TQ* __restrict_
     const int i = p * R + r;
     Sr[r] = (i < D && col < V) ? S[(size_t)i * V + col] : 0.f;
   }
-  for (int t0 = 0; t0 < qlen; t0 += TB) {
-    const int nt = min(TB, qlen - t0);
-    __syncthreads();                         // the staged tokens before are consumed
-    for (int e = tid; e < nt * DP; e += nthreads) {
+  auto stage = [&](int t0, int nt, float* buf) {          // straight into shared memory (the first batch)
+    for (int e = tid; e < nt * DP; e += LR_THREADS) {
       const int tt = e / DP, i = e % DP;
       const size_t row = (size_t)(tok0 + t0 + tt);
       const bool in = i < D;
-      qs[e] = in ? to_f32(q[row * ldq + (size_t)kvh * D + i]) * q_scale : 0.f;
-      ks[e] = in ? to_f32(k[row * ldk + (size_t)kvh * D + i]) : 0.f;
-      gs[e] = in ? decay[row * ldg + (size_t)h * D + i] : 0.f;
+      buf[e] = in ? to_f32(q[row * ldq + (size_t)kvh * D + i]) * q_scale : 0.f;
+      buf[TB * DP + e] = in ? to_f32(k[row * ldk + (size_t)kvh * D + i]) : 0.f;
+      buf[2 * TB * DP + e] = in ? decay[row * ldg + (size_t)h * D + i] : 0.f;
     }
-    for (int e = tid; e < nt * VB; e += nthreads) {
-      const int tt = e / VB, c = j0 + e % VB;
-      vs[e] = c < V ? to_f32(v[(size_t)(tok0 + t0 + tt) * ldv + (size_t)h * V + c]) : 0.f;
+    for (int e = tid; e < nt * CB; e += LR_THREADS) {
+      const int tt = e / CB, c = j0 + e % CB;
+      buf[3 * TB * DP + e] = c < V ? to_f32(v[(size_t)(tok0 + t0 + tt) * ldv + (size_t)h * V + c]) : 0.f;
     }
-    if (tid < nt) bs[tid] = DELTA ? beta[(size_t)(tok0 + t0 + tid) * ldb + h] : 1.f;
-    __syncthreads();
-    // k . q of each staged token: one warp per token, lanes stride over the channels
-    for (int tt = tid >> 5; tt < nt; tt += nthreads >> 5) {
-      float a = 0.f;
-      for (int i = tid & 31; i < DP; i += 32) a = fmaf(ks[tt * DP + i], qs[tt * DP + i], a);
-      a = warp_sum(a);
-      if ((tid & 31) == 0) kq[tt] = a;
-    }
-    __syncthreads();
+    if (tid < nt) buf[3 * TB * DP + TB * CB + tid] = DELTA ? beta[(size_t)(tok0 + t0 + tid) * ldb + h] : 1.f;
+  };
+  stage(0, min(TB, qlen), sm);
+  __syncthreads();
+  int cur = 0;
+  for (int t0 = 0; t0 < qlen; t0 += TB) {
+    const int nt = min(TB, qlen - t0);
+    const float* buf = sm + cur * BUF;
+    // the next batch goes to the other buffer while this one is worked on: its loads are issued here, by all
+    // threads, and nobody reads that buffer before the barrier at the end of this iteration
+    if (t0 + TB < qlen) stage(t0 + TB, min(TB, qlen - t0 - TB), sm + (cur ^ 1) * BUF);
+    const float* vs = buf + 3 * TB * DP;
+    const float* bs = vs + TB * CB;
     for (int tt = 0; tt < nt; ++tt) {
-      const float* qt = qs + tt * DP + p * R;
-      const float* kt = ks + tt * DP + p * R;
-      const float* gt = gs + tt * DP + p * R;
-      float a = 0.f, b = 0.f;               // (g S)^T k and (g S)^T q over this thread's rows
+      const float4* qt = reinterpret_cast<const float4*>(buf + tt * DP + p * R);
+      const float4* kt = reinterpret_cast<const float4*>(buf + TB * DP + tt * DP + p * R);
+      const float4* gt = reinterpret_cast<const float4*>(buf + 2 * TB * DP + tt * DP + p * R);
+      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f, c0 = 0.f, c1 = 0.f;   // (g S)^T k, (g S)^T q, k . q over this lane's rows
+      float kr[R];
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        Sr[r] *= gt[r];
-        a = fmaf(Sr[r], kt[r], a);
-        b = fmaf(Sr[r], qt[r], b);
+      for (int r4 = 0; r4 < R / 4; ++r4) {
+        const float4 g4 = gt[r4], k4 = kt[r4], q4 = qt[r4];
+        kr[4 * r4] = k4.x; kr[4 * r4 + 1] = k4.y; kr[4 * r4 + 2] = k4.z; kr[4 * r4 + 3] = k4.w;
+        Sr[4 * r4] *= g4.x; Sr[4 * r4 + 1] *= g4.y; Sr[4 * r4 + 2] *= g4.z; Sr[4 * r4 + 3] *= g4.w;
+        a0 = fmaf(Sr[4 * r4], k4.x, a0); a1 = fmaf(Sr[4 * r4 + 1], k4.y, a1);
+        a0 = fmaf(Sr[4 * r4 + 2], k4.z, a0); a1 = fmaf(Sr[4 * r4 + 3], k4.w, a1);
+        b0 = fmaf(Sr[4 * r4], q4.x, b0); b1 = fmaf(Sr[4 * r4 + 1], q4.y, b1);
+        b0 = fmaf(Sr[4 * r4 + 2], q4.z, b0); b1 = fmaf(Sr[4 * r4 + 3], q4.w, b1);
+        c0 = fmaf(k4.x, q4.x, c0); c1 = fmaf(k4.y, q4.y, c1);
+        c0 = fmaf(k4.z, q4.z, c0); c1 = fmaf(k4.w, q4.w, c1);
       }
-      if (P > 1) {
-        float* rd = red + (size_t)((t0 + tt) & 1) * 2 * P * VB;
-        rd[p * VB + j] = a;
-        rd[(P + p) * VB + j] = b;
-        __syncthreads();
-        a = 0.f;
-        b = 0.f;
-        for (int pp = 0; pp < P; ++pp) {
-          a += rd[pp * VB + j];
-          b += rd[(P + pp) * VB + j];
-        }
+      float a = a0 + a1, b = b0 + b1, c = c0 + c1;
+      for (int o = 1; o < P; o <<= 1) {       // the column's P lanes are neighbours: every lane ends with the sums
+        if (DELTA) a += __shfl_xor_sync(0xffffffffu, a, o);
+        b += __shfl_xor_sync(0xffffffffu, b, o);
+        c += __shfl_xor_sync(0xffffffffu, c, o);
       }
-      const float vj = vs[tt * VB + j];
+      const float vj = vs[tt * CB + cb];
       const float u = DELTA ? bs[tt] * (vj - a) : vj;
 #pragma unroll
-      for (int r = 0; r < R; ++r) Sr[r] = fmaf(kt[r], u, Sr[r]);
-      if (p == 0 && col < V) out[(size_t)(tok0 + t0 + tt) * ldo + (size_t)h * V + col] = fmaf(u, kq[tt], b);
+      for (int r = 0; r < R; ++r) Sr[r] = fmaf(kr[r], u, Sr[r]);
+      if (p == 0 && col < V) out[(size_t)(tok0 + t0 + tt) * ldo + (size_t)h * V + col] = fmaf(u, c, b);
     }
+    __syncthreads();     // the other buffer is filled, and this one is free for the batch after it
+    cur ^= 1;
   }
 #pragma unroll
   for (int r = 0; r < R; ++r) {
@@ -294,10 +296,13 @@ extern "C" int zi_linear_recurrence(float* out, int ldo, const void* q, int ldq,
   if (H <= 0 || G <= 0 || H % G) return zi_refuse("linear_recurrence: %d heads do not divide into %d key heads", H, G);
   if (D <= 0 || D > 512 || V <= 0) return zi_refuse("linear_recurrence: %d key channels (1..512), %d value channels", D, V);
   if (delta && !beta) return zi_refuse("linear_recurrence: the delta rule needs beta");
-  const int R = D <= 64 ? 16 : 32;
-  const int P = (D + R - 1) / R;
-  const size_t smem = (size_t)(3 * TB * P * R + TB * VB + 2 * TB + 4 * P * VB) * sizeof(float);
-  dim3 grid(n_seqs, H, (V + VB - 1) / VB), block(P * VB);
+  // R rows of a column per lane, P lanes per column (a power of two: the sums meet by a butterfly of shuffles)
+  const int R = D <= 256 ? 8 : 16;
+  int P = 1;
+  while (P * R < D) P <<= 1;
+  const int CB = LR_WARPS * (32 / P);
+  const size_t smem = (size_t)2 * (3 * TB * P * R + TB * CB + TB) * sizeof(float);
+  dim3 grid(n_seqs, H, (V + CB - 1) / CB), block(LR_THREADS);
 #define ZI_LR(TQ, TV, RR, DD)                                                                                          \
   do {                                                                                                                 \
     auto kern = linear_recurrence_kernel<TQ, TV, RR, DD>;                                                              \
@@ -310,8 +315,8 @@ extern "C" int zi_linear_recurrence(float* out, int ldo, const void* q, int ldq,
   } while (0)
 #define ZI_LR_R(TQ, TV)                                          \
   do {                                                           \
-    if (R == 16) { if (delta) ZI_LR(TQ, TV, 16, true); else ZI_LR(TQ, TV, 16, false); } \
-    else { if (delta) ZI_LR(TQ, TV, 32, true); else ZI_LR(TQ, TV, 32, false); }         \
+    if (R == 8) { if (delta) ZI_LR(TQ, TV, 8, true); else ZI_LR(TQ, TV, 8, false); } \
+    else { if (delta) ZI_LR(TQ, TV, 16, true); else ZI_LR(TQ, TV, 16, false); }         \
   } while (0)
   if (qk_dtype == ZI_F32 && v_dtype == ZI_F32) ZI_LR_R(float, float);
   else if (qk_dtype == ZI_BF16 && v_dtype == ZI_BF16) ZI_LR_R(__nv_bfloat16, __nv_bfloat16);

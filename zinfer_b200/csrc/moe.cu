@@ -197,11 +197,12 @@ moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, const flo
 // The router's product and the choice in one kernel, one block per token: the token's row in shared
 // memory as 32-bit values, a warp per router output (lanes stride over the row, partial sums meet in a
 // fixed order), then the first warp chooses.  32-bit multiply-adds whatever the operands' types.
-template <typename TX, typename TW>
+// GROUPED: the choice among groups of outputs (route_token_grouped) instead of the softmax with a correction.
+template <typename TX, typename TW, bool GROUPED>
 __global__ void __launch_bounds__(256)
 moe_router_kernel(int* __restrict__ chosen, float* __restrict__ weight, const TX* __restrict__ x, int ldx,
                   const TW* __restrict__ w, const float* __restrict__ correction, int K, int NR, int top,
-                  int renormalize) {
+                  int renormalize, int score_kind, int groups, int keep, float wscale) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float sm[];
@@ -241,7 +242,13 @@ moe_router_kernel(int* __restrict__ chosen, float* __restrict__ weight, const TX
     if (lane == 0) z[j] = acc;
   }
   __syncthreads();
-  if (warp == 0) route_token(chosen, weight, z, z + NR, z + 2 * NR, correction, t, NR, top, renormalize, lane);
+  if (warp == 0) {
+    if (GROUPED)
+      route_token_grouped(chosen, weight, z, z + NR, z + 2 * NR, z + 3 * NR, t, NR, top, renormalize, score_kind, groups, keep,
+                          wscale, lane);
+    else
+      route_token(chosen, weight, z, z + NR, z + 2 * NR, correction, t, NR, top, renormalize, lane);
+  }
 }
 
 // Few rows per expert (a decode step): out[r, n] = act(sum_k x[row_src[r], k] * w[e][n][k]) for the rows r of
@@ -438,29 +445,51 @@ extern "C" int zi_moe_route_grouped(int* chosen, float* weight, const float* log
   return zi_check_launch("moe_route_grouped");
 }
 
-extern "C" int zi_moe_router(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w, int w_dtype,
-                             const float* correction, int T, int K, int NR, int top, int renormalize,
-                             cudaStream_t stream) {
+static int launch_moe_router(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w, int w_dtype,
+                             const float* correction, int T, int K, int NR, int top, int renormalize, bool grouped,
+                             int score_kind, int groups, int keep, float wscale, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (top <= 0 || top > NR) return zi_refuse("moe_router: %d of %d outputs cannot be chosen", top, NR);
-  const size_t smem = (size_t)(K + 3 * NR) * sizeof(float);
+  if (grouped) {
+    if (groups <= 0 || NR % groups || keep <= 0 || keep > groups || top > keep * (NR / groups))
+      return zi_refuse("moe_router: %d of %d outputs in %d groups of which %d are kept", top, NR, groups, keep);
+    if (score_kind != 0 && score_kind != 1) return zi_refuse("moe_router: unknown score %d", score_kind);
+  }
+  const size_t smem = (size_t)(K + 4 * NR) * sizeof(float);
   if (smem > 200 * 1024) return zi_refuse("moe_router: rows of %d values and %d outputs are more than this kernel holds", K, NR);
   using bf = __nv_bfloat16;
-#define ZI_ROUTER(TX, TW)                                                                                          \
+#define ZI_ROUTER_G(TX, TW, GG)                                                                                    \
   do {                                                                                                             \
-    auto kern = moe_router_kernel<TX, TW>;                                                                         \
+    auto kern = moe_router_kernel<TX, TW, GG>;                                                                     \
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
       return zi_refuse("moe_router: cannot get %zu bytes of shared memory", smem);                                 \
     zi_launch(kern, dim3(T), dim3(256), smem, stream, chosen, weight, (const TX*)x, ldx, (const TW*)w, correction, K, NR, \
-              top, renormalize);                                                                                   \
+              top, renormalize, score_kind, groups, keep, wscale);                                                 \
   } while (0)
+#define ZI_ROUTER(TX, TW) do { if (grouped) ZI_ROUTER_G(TX, TW, true); else ZI_ROUTER_G(TX, TW, false); } while (0)
   if (x_dtype == ZI_F32 && w_dtype == ZI_F32) ZI_ROUTER(float, float);
   else if (x_dtype == ZI_F32 && w_dtype == ZI_BF16) ZI_ROUTER(float, bf);
   else if (x_dtype == ZI_BF16 && w_dtype == ZI_F32) ZI_ROUTER(bf, float);
   else if (x_dtype == ZI_BF16 && w_dtype == ZI_BF16) ZI_ROUTER(bf, bf);
   else return zi_refuse("moe_router: unknown dtype tags %d, %d", x_dtype, w_dtype);
 #undef ZI_ROUTER
+#undef ZI_ROUTER_G
   return zi_check_launch("moe_router");
+}
+
+extern "C" int zi_moe_router(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w, int w_dtype,
+                             const float* correction, int T, int K, int NR, int top, int renormalize,
+                             cudaStream_t stream) {
+  return launch_moe_router(chosen, weight, x, x_dtype, ldx, w, w_dtype, correction, T, K, NR, top, renormalize, false, 0, 1, 1,
+                           1.0f, stream);
+}
+
+// The router's product and the choice among groups of outputs (zi_moe_route_grouped) in one kernel.
+extern "C" int zi_moe_router_grouped(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w,
+                                     int w_dtype, int T, int K, int NR, int top, int renormalize, int score_kind,
+                                     int groups, int keep, float wscale, cudaStream_t stream) {
+  return launch_moe_router(chosen, weight, x, x_dtype, ldx, w, w_dtype, nullptr, T, K, NR, top, renormalize, true, score_kind,
+                           groups, keep, wscale, stream);
 }
 
 // Grouped product for tiles of 16 rows (see moe_few_rows_kernel).  x and w of one type (float32 or bfloat16),

@@ -1001,8 +1001,7 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
     dec_ok = fast and step.n_dec > 0 and L.zi_attention_mma_supported(num_heads, num_kv_heads, head_dim, 1)
     pf_ok = fast and step.n_pf_tiles > 0 and L.zi_attention_mma_supported(num_heads, num_kv_heads, head_dim, 0) \
         and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
-    if sink or (step.n_dec > 0 and not dec_ok) or (step.n_pf_tiles > 0 and not pf_ok):
-        # a softmax with a sink runs on the exact kernel (the tensor-core kernels have the plain softmax)
+    if (step.n_dec > 0 and not dec_ok) or (step.n_pf_tiles > 0 and not pf_ok):
         return paged_attention(q, k_cache, v_cache, block_tables, step.cu_q, step.kv_lens, step.tile_seq, step.tile_q0,
                                num_heads, num_kv_heads, head_dim, page_size, window, scale, sink=sink)
     _need(q.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous(), "attention: dense operands")
@@ -1012,6 +1011,27 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
     win = int(window or 0)
     work = lambda decode: _attention_work(step, decode, num_heads, num_kv_heads, head_dim, q.element_size()) \
         if _prof.ACTIVE is not None else (0, 0)
+    if sink:
+        # a softmax with a sink: the mma.sync kernels' form whose weights meet the values as two bfloat16 parts (a design
+        # that has a sink also wants its softmax weights in 32-bit) and whose denominator counts the sink
+        if step.n_pf_tiles > 0:
+            with _prof.region("attention (prefill, mma.sync, sink)", *work(False)):
+                _check(L.zi_attention_prefill_mma_sink(
+                    _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                    block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens), _ptr(step.pf_tile_seq), _ptr(step.pf_tile_q0),
+                    step.n_pf_tiles, num_heads, num_kv_heads, head_dim, page_size, win, ctypes.c_float(scale),
+                    ctypes.c_float(sink), _stream()), "attention (prefill, sink)")
+        if step.n_dec > 0:
+            splits = decode_splits(step.n_dec, num_kv_heads, _sm_count(q.device), step.max_kv_len)
+            need = L.zi_attention_decode_workspace_floats(step.n_dec, num_heads, num_kv_heads, head_dim, splits)
+            ws = torch.empty((need,), dtype=torch.float32, device=q.device) if need else None
+            with _prof.region("attention (decode, sink)", *work(True)):
+                _check(L.zi_attention_decode_mma_sink(
+                    _ptr(out), out.stride(0), _ptr(ws), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache),
+                    ctypes.c_longlong(k_cache.shape[0]), _ptr(block_tables), block_tables.stride(0), _ptr(step.cu_q),
+                    _ptr(step.kv_lens), _ptr(step.dec_seq), step.n_dec, num_heads, num_kv_heads, head_dim, page_size, win,
+                    ctypes.c_float(scale), splits, ctypes.c_float(sink), _stream()), "attention (decode, sink)")
+        return out
     if step.n_pf_tiles > 0 and PREFILL_ATTENTION == "tcgen05" and L.zi_attention_prefill_tcgen05_supported(
             num_heads, num_kv_heads, head_dim, page_size, _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache)):
         with _prof.region("attention (prefill, tcgen05)", *work(False)):
@@ -1317,6 +1337,24 @@ def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: torc
                                        _ptr(gate), _tag(gate), gate.stride(0), 0 if gate_kind == "silu" else 1, T, heads, vdim,
                                        _stream()), "head_norm_gate")
     return out
+
+
+def moe_router_grouped(x: torch.Tensor, w_router: torch.Tensor, top: int, score: str = "sigmoid", groups: int = 1, keep: int = 1,
+                       scale: float = 1.0, renormalize: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """The router's product (32-bit multiply-adds whatever the operands' types) and :func:`moe_route_grouped` in one
+    kernel, one block per token."""
+    T, K = x.shape
+    NR = w_router.shape[0]
+    _need(x.stride(1) == 1 and w_router.is_contiguous() and w_router.shape[1] == K, "moe_router: shapes")
+    _need(score in ("softmax", "sigmoid"), f"unknown router score {score!r}")
+    chosen = torch.empty((T, top), dtype=torch.int32, device=x.device)
+    weight = torch.empty((T, top), dtype=torch.float32, device=x.device)
+    with _prof.region(f"moe router (groups) N={NR} K={K}", lambda: _nb(w_router) + T * K * x.element_size(), 2 * T * NR * K):
+        _check(lib().zi_moe_router_grouped(_ptr(chosen), _ptr(weight), _ptr(x), _tag(x), x.stride(0), _ptr(w_router),
+                                           _tag(w_router), T, K, NR, top, 1 if renormalize else 0,
+                                           1 if score == "sigmoid" else 0, groups, keep, ctypes.c_float(scale), _stream()),
+               "moe_router_grouped")
+    return chosen, weight
 
 
 def moe_route_grouped(logits: torch.Tensor, top: int, score: str = "sigmoid", groups: int = 1, keep: int = 1,

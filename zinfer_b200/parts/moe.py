@@ -113,7 +113,10 @@ class RoutedExperts(FeedForward):
     def routed(self, x):
         T = x.shape[0]
         relu2 = not self.gated
-        if self.general_route:
+        if self.general_route and self.hidden <= 32768:
+            chosen, weight = ops.moe_router_grouped(x, self.w_router, self.top, self.score, self.groups, self.groups_kept,
+                                                    self.weight_scale, self.renormalize)
+        elif self.general_route:
             logits = ops.linear_cuda_cores(x, self.w_router, out_dtype=torch.float32)     # 32-bit multiply-adds
             chosen, weight = ops.moe_route_grouped(logits, self.top, self.score, self.groups, self.groups_kept,
                                                    self.weight_scale, self.renormalize)
