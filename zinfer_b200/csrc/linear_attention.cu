@@ -117,11 +117,13 @@ __global__ void sigmoid_rows_kernel(float* __restrict__ out, int ldo, const T* _
 
 // --------------------------------------------------------------------------- the recurrence
 // Block: one request, one head, CB neighbouring value channels; 8 warps.  A column of S (D key channels of one
-// value channel) belongs to P neighbouring lanes of one warp, R = 8 (or 16) rows each, in registers; the sums over
-// a column's rows meet by a butterfly of shuffles over those P lanes (a fixed order), so nothing in the loop over
-// tokens waits for another warp.  q, k and the decays of TB tokens at a time are staged in shared memory for the
-// whole block, the next TB tokens being fetched while these are worked on (one barrier per TB tokens).
-constexpr int LR_WARPS = 8, LR_THREADS = LR_WARPS * 32, TB = 16;
+// value channel) belongs to P neighbouring lanes of one warp, R = 8 (or 16) rows each, in registers, and every
+// lane works on NC = 2 columns at once (two independent chains of arithmetic per lane); the sums over a column's
+// rows meet by a butterfly of shuffles over those P lanes (a fixed order), so nothing in the loop over tokens
+// waits for another warp.  q, k and the decays of TB tokens at a time are staged in shared memory for the whole
+// block, laid out so that the lanes' 16-byte reads fall into different banks; the next TB tokens are fetched
+// into registers while these are worked on and stored afterwards (one barrier per TB tokens).
+constexpr int LR_WARPS = 8, LR_THREADS = LR_WARPS * 32, TB = 16, NC = 2;
 
 template <typename TQ, typename TV, int R, bool DELTA>
 __global__ void __launch_bounds__(LR_THREADS)
@@ -133,87 +135,160 @@ linear_recurrence_kernel(float* __restrict__ out, int ldo, const TQ* __restrict_
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float sm[];
-  const int DP = P * R;                      // key channels rounded up to whole parts
-  const int CW = 32 / P, CB = LR_WARPS * CW; // columns per warp and per block
-  const int BUF = 3 * TB * DP + TB * CB + TB;   // one staging buffer: q, k, g [TB][DP], v [TB][CB], beta [TB]
+  const int DP = P * R;                           // key channels rounded up to whole parts
+  const int CW = (32 / P) * NC, CB = LR_WARPS * CW;   // columns per warp and per block
+  const int BUF = 3 * TB * DP + TB * CB + TB;     // one staging buffer: q, k, g [TB][DP], v [TB][CB], beta [TB]
   const int s = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * CB;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int p = lane % P, cw = lane / P;
-  const int cb = warp * CW + cw, col = j0 + cb;     // column within the block, and of the head
+  const int cb = warp * CW + cw * NC, col = j0 + cb;   // this lane's first column within the block, and of the head
   const int kvh = h / (H / G);
   const int tok0 = cu_q[s], qlen = cu_q[s + 1] - tok0;
   if (qlen <= 0) return;
   float* S = state + (size_t)state_slots[s] * slot_stride + (size_t)h * D * V;
-  float Sr[R];
+  float Sr[NC][R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const int i = p * R + r;
-    Sr[r] = (i < D && col < V) ? S[(size_t)i * V + col] : 0.f;
-  }
-  auto stage = [&](int t0, int nt, float* buf) {          // straight into shared memory (the first batch)
-    for (int e = tid; e < nt * DP; e += LR_THREADS) {
-      const int tt = e / DP, i = e % DP;
+  for (int c = 0; c < NC; ++c)
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int i = p * R + r;
+      Sr[c][r] = (i < D && col + c < V) ? S[(size_t)i * V + col + c] : 0.f;
+    }
+  // DP and CB are powers of two: shifts instead of divisions
+  const int lgDP = 31 - __clz(DP), lgCB = 31 - __clz(CB), lgP = 31 - __clz(P);
+  // Key channel i = p R + 4 r4 + x lies at ((r4 P + p) 4 + x) of its token's row: for one r4 the P lanes of a column
+  // read neighbouring 16-byte pieces.
+  constexpr int LGR = R == 8 ? 3 : 4;
+  auto place = [&](int i) { return ((((i >> 2) & (R / 4 - 1)) << lgP) + (i >> LGR)) * 4 + (i & 3); };
+  // Staging in two halves: fetch() takes the first NPF elements per thread of q, k and the decays (all of them
+  // while DP <= 128) and the first two of v into registers as they are stored; put() widens and stores them, and
+  // fetches and stores whatever is left beyond them.
+  constexpr int NPF = 8, NPV = 2;
+  TQ fq[NPF], fk[NPF];
+  TV fv[NPV];
+  float fg[NPF], fb = 1.f;
+  auto fetch = [&](int t0, int nt) {
+    const int total = nt << lgDP;
+#pragma unroll
+    for (int u = 0; u < NPF; ++u) {
+      const int e = tid + u * LR_THREADS;
+      const int tt = e >> lgDP, i = e & (DP - 1);
+      if (e < total && i < D) {
+        const size_t row = (size_t)(tok0 + t0 + tt);
+        fq[u] = q[row * ldq + (size_t)kvh * D + i];
+        fk[u] = k[row * ldk + (size_t)kvh * D + i];
+        fg[u] = decay[row * ldg + (size_t)h * D + i];
+      } else {
+        fq[u] = from_f32<TQ>(0.f);
+        fk[u] = from_f32<TQ>(0.f);
+        fg[u] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < NPV; ++u) {
+      const int e = tid + u * LR_THREADS;
+      const int c = j0 + (e & (CB - 1));
+      fv[u] = (e < (nt << lgCB) && c < V) ? v[(size_t)(tok0 + t0 + (e >> lgCB)) * ldv + (size_t)h * V + c] : from_f32<TV>(0.f);
+    }
+    if (DELTA && tid < nt) fb = beta[(size_t)(tok0 + t0 + tid) * ldb + h];
+  };
+  auto put = [&](int t0, int nt, float* buf) {
+    const int total = nt << lgDP;
+#pragma unroll
+    for (int u = 0; u < NPF; ++u) {
+      const int e = tid + u * LR_THREADS;
+      if (e < total) {
+        const int at = (e & ~(DP - 1)) + place(e & (DP - 1));
+        buf[at] = to_f32(fq[u]) * q_scale;
+        buf[TB * DP + at] = to_f32(fk[u]);
+        buf[2 * TB * DP + at] = fg[u];
+      }
+    }
+    for (int e = tid + NPF * LR_THREADS; e < total; e += LR_THREADS) {      // beyond the registers (DP > 128)
+      const int tt = e >> lgDP, i = e & (DP - 1);
       const size_t row = (size_t)(tok0 + t0 + tt);
       const bool in = i < D;
-      buf[e] = in ? to_f32(q[row * ldq + (size_t)kvh * D + i]) * q_scale : 0.f;
-      buf[TB * DP + e] = in ? to_f32(k[row * ldk + (size_t)kvh * D + i]) : 0.f;
-      buf[2 * TB * DP + e] = in ? decay[row * ldg + (size_t)h * D + i] : 0.f;
+      const int at = (e & ~(DP - 1)) + place(i);
+      buf[at] = in ? to_f32(q[row * ldq + (size_t)kvh * D + i]) * q_scale : 0.f;
+      buf[TB * DP + at] = in ? to_f32(k[row * ldk + (size_t)kvh * D + i]) : 0.f;
+      buf[2 * TB * DP + at] = in ? decay[row * ldg + (size_t)h * D + i] : 0.f;
     }
-    for (int e = tid; e < nt * CB; e += LR_THREADS) {
-      const int tt = e / CB, c = j0 + e % CB;
-      buf[3 * TB * DP + e] = c < V ? to_f32(v[(size_t)(tok0 + t0 + tt) * ldv + (size_t)h * V + c]) : 0.f;
+#pragma unroll
+    for (int u = 0; u < NPV; ++u) {
+      const int e = tid + u * LR_THREADS;
+      if (e < (nt << lgCB)) buf[3 * TB * DP + e] = to_f32(fv[u]);
     }
-    if (tid < nt) buf[3 * TB * DP + TB * CB + tid] = DELTA ? beta[(size_t)(tok0 + t0 + tid) * ldb + h] : 1.f;
+    for (int e = tid + NPV * LR_THREADS; e < (nt << lgCB); e += LR_THREADS) {
+      const int c = j0 + (e & (CB - 1));
+      buf[3 * TB * DP + e] = c < V ? to_f32(v[(size_t)(tok0 + t0 + (e >> lgCB)) * ldv + (size_t)h * V + c]) : 0.f;
+    }
+    if (tid < nt) buf[3 * TB * DP + TB * CB + tid] = fb;
   };
-  stage(0, min(TB, qlen), sm);
+  fetch(0, min(TB, qlen));
+  put(0, min(TB, qlen), sm);
   __syncthreads();
   int cur = 0;
   for (int t0 = 0; t0 < qlen; t0 += TB) {
     const int nt = min(TB, qlen - t0);
     const float* buf = sm + cur * BUF;
-    // the next batch goes to the other buffer while this one is worked on: its loads are issued here, by all
-    // threads, and nobody reads that buffer before the barrier at the end of this iteration
-    if (t0 + TB < qlen) stage(t0 + TB, min(TB, qlen - t0 - TB), sm + (cur ^ 1) * BUF);
+    // the next batch's loads go out now and land in the other buffer after this batch's work; nobody reads that
+    // buffer before the barrier at the end of this iteration
+    const bool more = t0 + TB < qlen;
+    if (more) fetch(t0 + TB, min(TB, qlen - t0 - TB));
     const float* vs = buf + 3 * TB * DP;
     const float* bs = vs + TB * CB;
     for (int tt = 0; tt < nt; ++tt) {
-      const float4* qt = reinterpret_cast<const float4*>(buf + tt * DP + p * R);
-      const float4* kt = reinterpret_cast<const float4*>(buf + TB * DP + tt * DP + p * R);
-      const float4* gt = reinterpret_cast<const float4*>(buf + 2 * TB * DP + tt * DP + p * R);
-      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f, c0 = 0.f, c1 = 0.f;   // (g S)^T k, (g S)^T q, k . q over this lane's rows
+      const float4* qt = reinterpret_cast<const float4*>(buf + tt * DP) + p;
+      const float4* kt = reinterpret_cast<const float4*>(buf + TB * DP + tt * DP) + p;
+      const float4* gt = reinterpret_cast<const float4*>(buf + 2 * TB * DP + tt * DP) + p;
+      float a[NC], b[NC], kq = 0.f;      // (g S)^T k and (g S)^T q per column, k . q, over this lane's rows
+#pragma unroll
+      for (int c = 0; c < NC; ++c) a[c] = b[c] = 0.f;
       float kr[R];
 #pragma unroll
       for (int r4 = 0; r4 < R / 4; ++r4) {
-        const float4 g4 = gt[r4], k4 = kt[r4], q4 = qt[r4];
+        const float4 g4 = gt[r4 << lgP], k4 = kt[r4 << lgP], q4 = qt[r4 << lgP];
         kr[4 * r4] = k4.x; kr[4 * r4 + 1] = k4.y; kr[4 * r4 + 2] = k4.z; kr[4 * r4 + 3] = k4.w;
-        Sr[4 * r4] *= g4.x; Sr[4 * r4 + 1] *= g4.y; Sr[4 * r4 + 2] *= g4.z; Sr[4 * r4 + 3] *= g4.w;
-        a0 = fmaf(Sr[4 * r4], k4.x, a0); a1 = fmaf(Sr[4 * r4 + 1], k4.y, a1);
-        a0 = fmaf(Sr[4 * r4 + 2], k4.z, a0); a1 = fmaf(Sr[4 * r4 + 3], k4.w, a1);
-        b0 = fmaf(Sr[4 * r4], q4.x, b0); b1 = fmaf(Sr[4 * r4 + 1], q4.y, b1);
-        b0 = fmaf(Sr[4 * r4 + 2], q4.z, b0); b1 = fmaf(Sr[4 * r4 + 3], q4.w, b1);
-        c0 = fmaf(k4.x, q4.x, c0); c1 = fmaf(k4.y, q4.y, c1);
-        c0 = fmaf(k4.z, q4.z, c0); c1 = fmaf(k4.w, q4.w, c1);
-      }
-      float a = a0 + a1, b = b0 + b1, c = c0 + c1;
-      for (int o = 1; o < P; o <<= 1) {       // the column's P lanes are neighbours: every lane ends with the sums
-        if (DELTA) a += __shfl_xor_sync(0xffffffffu, a, o);
-        b += __shfl_xor_sync(0xffffffffu, b, o);
-        c += __shfl_xor_sync(0xffffffffu, c, o);
-      }
-      const float vj = vs[tt * CB + cb];
-      const float u = DELTA ? bs[tt] * (vj - a) : vj;
+        kq = fmaf(k4.x, q4.x, fmaf(k4.y, q4.y, fmaf(k4.z, q4.z, fmaf(k4.w, q4.w, kq))));
 #pragma unroll
-      for (int r = 0; r < R; ++r) Sr[r] = fmaf(kr[r], u, Sr[r]);
-      if (p == 0 && col < V) out[(size_t)(tok0 + t0 + tt) * ldo + (size_t)h * V + col] = fmaf(u, c, b);
+        for (int c = 0; c < NC; ++c) {
+          float* sr = Sr[c] + 4 * r4;
+          sr[0] *= g4.x; sr[1] *= g4.y; sr[2] *= g4.z; sr[3] *= g4.w;
+          if (DELTA) a[c] = fmaf(sr[0], k4.x, fmaf(sr[1], k4.y, fmaf(sr[2], k4.z, fmaf(sr[3], k4.w, a[c]))));
+          b[c] = fmaf(sr[0], q4.x, fmaf(sr[1], q4.y, fmaf(sr[2], q4.z, fmaf(sr[3], q4.w, b[c]))));
+        }
+      }
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {       // the column's P lanes are neighbours: every lane ends with the sums
+        if (o < P) {
+#pragma unroll
+          for (int c = 0; c < NC; ++c) {
+            if (DELTA) a[c] += __shfl_xor_sync(0xffffffffu, a[c], o);
+            b[c] += __shfl_xor_sync(0xffffffffu, b[c], o);
+          }
+          kq += __shfl_xor_sync(0xffffffffu, kq, o);
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        const float vj = vs[tt * CB + cb + c];
+        const float u = DELTA ? bs[tt] * (vj - a[c]) : vj;
+#pragma unroll
+        for (int r = 0; r < R; ++r) Sr[c][r] = fmaf(kr[r], u, Sr[c][r]);
+        if (p == 0 && col + c < V) out[(size_t)(tok0 + t0 + tt) * ldo + (size_t)h * V + col + c] = fmaf(u, kq, b[c]);
+      }
     }
+    if (more) put(t0 + TB, min(TB, qlen - t0 - TB), sm + (cur ^ 1) * BUF);
     __syncthreads();     // the other buffer is filled, and this one is free for the batch after it
     cur ^= 1;
   }
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const int i = p * R + r;
-    if (i < D && col < V) S[(size_t)i * V + col] = Sr[r];
-  }
+  for (int c = 0; c < NC; ++c)
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int i = p * R + r;
+      if (i < D && col + c < V) S[(size_t)i * V + col + c] = Sr[c][r];
+    }
 }
 
 // ----------------------------------------------------------------------- gated per-head norm
@@ -300,7 +375,7 @@ extern "C" int zi_linear_recurrence(float* out, int ldo, const void* q, int ldq,
   const int R = D <= 256 ? 8 : 16;
   int P = 1;
   while (P * R < D) P <<= 1;
-  const int CB = LR_WARPS * (32 / P);
+  const int CB = LR_WARPS * (32 / P) * NC;
   const size_t smem = (size_t)2 * (3 * TB * P * R + TB * CB + TB) * sizeof(float);
   dim3 grid(n_seqs, H, (V + CB - 1) / CB), block(LR_THREADS);
 #define ZI_LR(TQ, TV, RR, DD)                                                                                          \
