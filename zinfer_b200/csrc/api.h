@@ -123,9 +123,11 @@ int zi_qk_prepare(const void* src, int dtype, int T, int src_stride, void* q_out
                   int n_table_pos, const int* positions, void* kcache, void* vcache, const int* slots, int page_size,
                   int v_from_k, int write_kv, cudaStream_t stream);
 int zi_rope_table_scaled(float* cos_t, float* sin_t, int n_pos, int d, float theta, float factor, cudaStream_t stream);
-// h += norm(sa * a + sb * b) * w (the norm of a sublayer's output), x_out = h in the activations' type.
-int zi_norm_residual(float* h, const void* a, int a_dtype, float sa, const void* b, int b_dtype, float sb, const float* w,
-                     float eps, void* x_out, int out_dtype, int T, int H, cudaStream_t stream);
+// h += norm(sa * a + sb * b) * w (the norm of a sublayer's output), x_out = h in the activations' type; a and b whole
+// or as split-K partial sums [splits][T][H].
+int zi_norm_residual(float* h, const void* a, int a_dtype, const float* a_part, int a_splits, long long a_zstride, float sa,
+                     const void* b, int b_dtype, const float* b_part, int b_splits, long long b_zstride, float sb,
+                     const float* w, float eps, void* x_out, int out_dtype, int T, int H, cudaStream_t stream);
 int zi_cast_rows(void* out, int out_dtype, const float* h, long long n, cudaStream_t stream);
 int zi_relu2(void* x, int dtype, long long n, cudaStream_t stream);
 // Mixers with a matrix-valued state per head (linear attention with decays, with or without the delta rule).

@@ -846,40 +846,78 @@ extern "C" int zi_qk_prepare(const void* src, int dtype, int T, int src_stride, 
 }
 
 // ------------------------------------------- norm of a sublayer's OUTPUT, then the residual sum
-// h += norm(sa * a + sb * b) * w with norm(y) = y / sqrt(mean(y^2) + eps); x_out = h in the activations'
-// type (what the next sublayer reads).  b may be absent.  One block per row, 32-bit throughout.
+// h += norm(sa * a + sb * b) * w with norm(y) = y / sqrt(mean(y^2) + eps); x_out = h in the activations' type
+// (what the next sublayer reads).  b may be absent.  a and b each come whole or as split-K partial sums
+// part[z][row][H] that are added in order.  One block per row, 32-bit throughout.
+template <typename TA, typename TB>
+__device__ __forceinline__ float update_at(const TA* a, const float* ap, int as, size_t az, float sa, const TB* b, const float* bp,
+                                           int bs, size_t bz, float sb, bool has_b, size_t at) {
+  float va;
+  if (ap) {
+    va = 0.f;
+    for (int z = 0; z < as; ++z) va += ap[(size_t)z * az + at];
+  } else {
+    va = to_f32(a[at]);
+  }
+  float y = sa * va;
+  if (has_b) {
+    float vb;
+    if (bp) {
+      vb = 0.f;
+      for (int z = 0; z < bs; ++z) vb += bp[(size_t)z * bz + at];
+    } else {
+      vb = to_f32(b[at]);
+    }
+    y = fmaf(sb, vb, y);
+  }
+  return y;
+}
+
 template <typename TA, typename TB, typename TO>
 __global__ void __launch_bounds__(256)
-norm_residual_kernel(float* __restrict__ h, const TA* __restrict__ a, float sa, const TB* __restrict__ b, float sb,
+norm_residual_kernel(float* __restrict__ h, const TA* __restrict__ a, const float* __restrict__ ap, int as, size_t az, float sa,
+                     const TB* __restrict__ b, const float* __restrict__ bp, int bs, size_t bz, float sb,
                      const float* __restrict__ w, float eps, TO* __restrict__ x_out, int H) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float scratch[33];
+  extern __shared__ float ys[];          // the row's summed update (H floats), so that partial sums are read once
   const size_t row = (size_t)blockIdx.x * H;
+  const bool has_b = b != nullptr || bp != nullptr;
   float ss = 0.f;
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    float y = sa * to_f32(a[row + c]);
-    if (b) y = fmaf(sb, to_f32(b[row + c]), y);
+    const float y = update_at(a, ap, as, az, sa, b, bp, bs, bz, sb, has_b, row + c);
+    ys[c] = y;
     ss = fmaf(y, y, ss);
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)H + eps);
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    float y = sa * to_f32(a[row + c]);
-    if (b) y = fmaf(sb, to_f32(b[row + c]), y);
-    const float v = h[row + c] + y * inv * w[c];
+    const float v = h[row + c] + ys[c] * inv * w[c];
     h[row + c] = v;
     if (x_out) x_out[row + c] = from_f32<TO>(v);
   }
 }
 
-extern "C" int zi_norm_residual(float* h, const void* a, int a_dtype, float sa, const void* b, int b_dtype, float sb,
-                                const float* w, float eps, void* x_out, int out_dtype, int T, int H, cudaStream_t stream) {
+extern "C" int zi_norm_residual(float* h, const void* a, int a_dtype, const float* a_part, int a_splits, long long a_zstride,
+                                float sa, const void* b, int b_dtype, const float* b_part, int b_splits, long long b_zstride,
+                                float sb, const float* w, float eps, void* x_out, int out_dtype, int T, int H,
+                                cudaStream_t stream) {
   if (T <= 0 || H <= 0) return 0;
-  if (!a) return zi_refuse("norm_residual: no update given");
-  ZI_DISPATCH_DTYPE(a_dtype, TA, ZI_DISPATCH_DTYPE(b ? b_dtype : ZI_F32, TB, ZI_DISPATCH_DTYPE(out_dtype, TO,
-      zi_launch(norm_residual_kernel<TA, TB, TO>, dim3(T), dim3(256), 0, stream, h, (const TA*)a, sa, (const TB*)b, sb, w, eps,
-                (TO*)x_out, H))));
+  if ((a == nullptr) == (a_part == nullptr)) return zi_refuse("norm_residual: give the update either whole or as partial sums");
+  if (b && b_part) return zi_refuse("norm_residual: give the second update either whole or as partial sums");
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 200 * 1024) return zi_refuse("norm_residual: rows of %d values are more than this kernel holds", H);
+#define ZI_NR(TA, TB, TO)                                                                                               \
+  do {                                                                                                                  \
+    auto kern = norm_residual_kernel<TA, TB, TO>;                                                                       \
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+      return zi_refuse("norm_residual: cannot get %zu bytes of shared memory", smem);                                   \
+    zi_launch(kern, dim3(T), dim3(256), smem, stream, h, (const TA*)a, a_part, a_splits, (size_t)a_zstride, sa, (const TB*)b, \
+              b_part, b_splits, (size_t)b_zstride, sb, w, eps, (TO*)x_out, H);                                          \
+  } while (0)
+  ZI_DISPATCH_DTYPE(a ? a_dtype : ZI_F32, TA, ZI_DISPATCH_DTYPE(b ? b_dtype : ZI_F32, TB, ZI_DISPATCH_DTYPE(out_dtype, TO, ZI_NR(TA, TB, TO))));
+#undef ZI_NR
   return zi_check_launch("norm_residual");
 }
 

@@ -1163,30 +1163,32 @@ def attention_decode_fused(qkv, num_heads: int, num_kv_heads: int, head_dim: int
 
 
 # ------------------------------------------------- norm of a sublayer's output, small elementwise
-def _whole(delta, dtype=torch.float32):
-    """(tensor, multiplier) of an update given as a tensor, :class:`Partials` or :class:`Scaled`."""
-    delta, scale = _unscaled(delta)
-    if isinstance(delta, Partials):
-        delta = delta.sum(dtype)
-    return delta, scale
-
-
 def norm_residual(h: torch.Tensor, a, weight: torch.Tensor, eps: float, out_dtype: torch.dtype, b=None) -> torch.Tensor:
     """``h += rmsnorm(a + b) * weight`` in place, the norm taken over the sublayer's OUTPUT (``a``, and ``b`` if given:
-    tensors, :class:`Partials`, or either inside :class:`Scaled`).  Returns ``h`` in ``out_dtype``: what the next
-    sublayer reads (``h`` itself for float32)."""
+    tensors, :class:`Partials` whose splits the kernel adds in order, or either inside :class:`Scaled`).  Returns ``h``
+    in ``out_dtype``: what the next sublayer reads (``h`` itself for float32)."""
     T, H = h.shape
-    a, sa = _whole(a)
-    b, sb = _whole(b) if b is not None else (None, 0.0)
     _need(h.dtype == torch.float32 and h.is_contiguous(), "the residual stream is contiguous float32")
     _need(weight.dtype == torch.float32 and weight.numel() == H, "norm weight must be float32 of the row's width")
-    for t in (a, b):
-        if t is not None:
-            _need(tuple(t.shape) == (T, H) and t.is_contiguous(), "an update must match the residual stream")
+
+    def operand(delta):
+        """(tensor, tag, partial sums, splits, stride between splits, multiplier)"""
+        if delta is None:
+            return None, F32, None, 0, 0, 0.0
+        delta, scale = _unscaled(delta)
+        if isinstance(delta, Partials):
+            _need(tuple(delta.shape) == (T, H), "an update must match the residual stream")
+            return None, F32, delta.data, delta.splits, T * H, scale
+        _need(tuple(delta.shape) == (T, H) and delta.is_contiguous(), "an update must match the residual stream")
+        return delta, _tag(delta), None, 0, 0, scale
+
+    at, atag, ap, asplits, az, sa = operand(a)
+    bt, btag, bp, bsplits, bz, sb = operand(b)
+    _need(at is not None or ap is not None, "norm_residual: no update given")
     x = None if out_dtype == torch.float32 else torch.empty((T, H), dtype=out_dtype, device=h.device)
-    with _prof.region("norm of the output + residual add", lambda: 2 * _nb(h) + 2 * _nb(a, b) + _nb(x)):
-        _check(lib().zi_norm_residual(_ptr(h), _ptr(a), _tag(a), ctypes.c_float(sa), _ptr(b), _tag(b) if b is not None else F32,
-                                      ctypes.c_float(sb), _ptr(weight), ctypes.c_float(eps), _ptr(x),
+    with _prof.region("norm of the output + residual add", lambda: 2 * _nb(h) + _nb(at, bt, ap, bp, x)):
+        _check(lib().zi_norm_residual(_ptr(h), _ptr(at), atag, _ptr(ap), asplits, _ll(az), ctypes.c_float(sa), _ptr(bt), btag,
+                                      _ptr(bp), bsplits, _ll(bz), ctypes.c_float(sb), _ptr(weight), ctypes.c_float(eps), _ptr(x),
                                       _tag(x) if x is not None else F32, T, H, _stream()), "norm_residual")
     return h if x is None else x
 
