@@ -849,32 +849,54 @@ extern "C" int zi_qk_prepare(const void* src, int dtype, int T, int src_stride, 
 // h += norm(sa * a + sb * b) * w with norm(y) = y / sqrt(mean(y^2) + eps); x_out = h in the activations' type
 // (what the next sublayer reads).  b may be absent.  a and b each come whole or as split-K partial sums
 // part[z][row][H] that are added in order.  One block per row, 32-bit throughout.
-template <typename TA, typename TB>
-__device__ __forceinline__ float update_at(const TA* a, const float* ap, int as, size_t az, float sa, const TB* b, const float* bp,
-                                           int bs, size_t bz, float sb, bool has_b, size_t at) {
-  float va;
-  if (ap) {
-    va = 0.f;
-    for (int z = 0; z < as; ++z) va += ap[(size_t)z * az + at];
-  } else {
-    va = to_f32(a[at]);
+// one operand's value at `at`: whole, or the sum of its partial sums in order, four loads in flight
+template <typename TA>
+__device__ __forceinline__ float operand_at(const TA* a, const float* ap, int as, size_t az, size_t at) {
+  if (!ap) return to_f32(a[at]);
+  const float* p = ap + at;
+  float v = 0.f;
+  int z = 0;
+  for (; z + 4 <= as; z += 4) {
+    const float p0 = p[(size_t)z * az], p1 = p[(size_t)(z + 1) * az], p2 = p[(size_t)(z + 2) * az], p3 = p[(size_t)(z + 3) * az];
+    v = (((v + p0) + p1) + p2) + p3;
   }
-  float y = sa * va;
-  if (has_b) {
-    float vb;
-    if (bp) {
-      vb = 0.f;
-      for (int z = 0; z < bs; ++z) vb += bp[(size_t)z * bz + at];
-    } else {
-      vb = to_f32(b[at]);
-    }
-    y = fmaf(sb, vb, y);
-  }
-  return y;
+  for (; z < as; ++z) v += p[(size_t)z * az];
+  return v;
 }
 
+// Many rows (a prompt): the GPU is full of rows, a block of 256 threads reads its row's update twice (the second time
+// from cache) and keeps nothing in shared memory.
 template <typename TA, typename TB, typename TO>
 __global__ void __launch_bounds__(256)
+norm_residual_rows_kernel(float* __restrict__ h, const TA* __restrict__ a, const float* __restrict__ ap, int as, size_t az, float sa,
+                          const TB* __restrict__ b, const float* __restrict__ bp, int bs, size_t bz, float sb,
+                          const float* __restrict__ w, float eps, TO* __restrict__ x_out, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const size_t row = (size_t)blockIdx.x * H;
+  const bool has_b = b != nullptr || bp != nullptr;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float y = sa * operand_at(a, ap, as, az, row + c);
+    if (has_b) y = fmaf(sb, operand_at(b, bp, bs, bz, row + c), y);
+    ss = fmaf(y, y, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float y = sa * operand_at(a, ap, as, az, row + c);
+    if (has_b) y = fmaf(sb, operand_at(b, bp, bs, bz, row + c), y);
+    const float v = h[row + c] + y * inv * w[c];
+    h[row + c] = v;
+    if (x_out) x_out[row + c] = from_f32<TO>(v);
+  }
+}
+
+// Few rows (a decode step): a row's loads are spread over up to 1024 threads, four columns of a thread in flight
+// together, and the summed update is kept in shared memory so that partial sums are read once.
+template <typename TA, typename TB, typename TO>
+__global__ void __launch_bounds__(1024)
 norm_residual_kernel(float* __restrict__ h, const TA* __restrict__ a, const float* __restrict__ ap, int as, size_t az, float sa,
                      const TB* __restrict__ b, const float* __restrict__ bp, int bs, size_t bz, float sb,
                      const float* __restrict__ w, float eps, TO* __restrict__ x_out, int H) {
@@ -885,10 +907,26 @@ norm_residual_kernel(float* __restrict__ h, const TA* __restrict__ a, const floa
   const size_t row = (size_t)blockIdx.x * H;
   const bool has_b = b != nullptr || bp != nullptr;
   float ss = 0.f;
-  for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    const float y = update_at(a, ap, as, az, sa, b, bp, bs, bz, sb, has_b, row + c);
-    ys[c] = y;
-    ss = fmaf(y, y, ss);
+  // four columns of a thread at a time: their loads (and those of their partial sums) are in flight together
+  for (int c0 = threadIdx.x; c0 < H; c0 += 4 * blockDim.x) {
+    float y[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + u * blockDim.x;
+      y[u] = 0.f;
+      if (c < H) {
+        y[u] = sa * operand_at(a, ap, as, az, row + c);
+        if (has_b) y[u] = fmaf(sb, operand_at(b, bp, bs, bz, row + c), y[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + u * blockDim.x;
+      if (c < H) {
+        ys[c] = y[u];
+        ss = fmaf(y[u], y[u], ss);
+      }
+    }
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)H + eps);
@@ -908,12 +946,19 @@ extern "C" int zi_norm_residual(float* h, const void* a, int a_dtype, const floa
   if (b && b_part) return zi_refuse("norm_residual: give the second update either whole or as partial sums");
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 200 * 1024) return zi_refuse("norm_residual: rows of %d values are more than this kernel holds", H);
+  // few rows (a decode step): a row's loads are spread over as many threads as it has columns in fours; many rows fill the GPU anyway
+  const int threads = H >= 4096 ? 1024 : (H >= 2048 ? 512 : 256);
 #define ZI_NR(TA, TB, TO)                                                                                               \
   do {                                                                                                                  \
+    if (T > 512) {                                                                                                      \
+      zi_launch(norm_residual_rows_kernel<TA, TB, TO>, dim3(T), dim3(256), 0, stream, h, (const TA*)a, a_part, a_splits, \
+                (size_t)a_zstride, sa, (const TB*)b, b_part, b_splits, (size_t)b_zstride, sb, w, eps, (TO*)x_out, H);   \
+      break;                                                                                                            \
+    }                                                                                                                   \
     auto kern = norm_residual_kernel<TA, TB, TO>;                                                                       \
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
       return zi_refuse("norm_residual: cannot get %zu bytes of shared memory", smem);                                   \
-    zi_launch(kern, dim3(T), dim3(256), smem, stream, h, (const TA*)a, a_part, a_splits, (size_t)a_zstride, sa, (const TB*)b, \
+    zi_launch(kern, dim3(T), dim3(threads), smem, stream, h, (const TA*)a, a_part, a_splits, (size_t)a_zstride, sa, (const TB*)b, \
               b_part, b_splits, (size_t)b_zstride, sb, w, eps, (TO*)x_out, H);                                          \
   } while (0)
   ZI_DISPATCH_DTYPE(a ? a_dtype : ZI_F32, TA, ZI_DISPATCH_DTYPE(b ? b_dtype : ZI_F32, TB, ZI_DISPATCH_DTYPE(out_dtype, TO, ZI_NR(TA, TB, TO))));
