@@ -475,6 +475,23 @@ def test_small_kernels_against_plain_formulas():
     h_dev = h.to(DEV)
     x = ops.norm_residual(h_dev, ops.Scaled(a.to(DEV), 0.7), wt.to(DEV), 1e-5, torch.bfloat16, b=ops.Scaled(b.to(DEV), 1.3))
     assert torch.allclose(h_dev.cpu(), want_h, rtol=1e-5, atol=1e-6) and torch.equal(x.cpu(), h_dev.cpu().to(torch.bfloat16))
+    # the same in its other forms: many rows (16-byte accesses; widths that do not allow them), updates in bfloat16,
+    # updates as split-K partial sums over few rows, one update only; relu^2 with and without 16-byte accesses
+    for T, H, parts in ((600, 48, 0), (600, 43, 0), (5, 4100, 3), (520, 36, 2), (3, 52, 0)):
+        h, wt = r(T, H), 1 + 0.1 * r(H)
+        a = r(parts, T, H) if parts else r(T, H).to(torch.bfloat16)
+        for b in (None, r(T, H)):
+            want_h = h.clone()
+            ref.norm_residual(want_h, ref.Scaled(a.sum(0) if parts else a, 0.7), wt, 1e-5, torch.float32,
+                              b=None if b is None else ref.Scaled(b, 1.3))
+            h_dev = h.to(DEV)
+            x = ops.norm_residual(h_dev, ops.Scaled(ops.Partials(a.to(DEV)) if parts else a.to(DEV), 0.7), wt.to(DEV), 1e-5,
+                                  torch.bfloat16, b=None if b is None else ops.Scaled(b.to(DEV), 1.3))
+            assert torch.allclose(h_dev.cpu(), want_h, rtol=1e-5, atol=2e-6), (T, H, parts, b is None)
+            assert torch.equal(x.cpu(), h_dev.cpu().to(torch.bfloat16))
+    for n, dt in ((4096, torch.bfloat16), (37, torch.float32), (1028, torch.float32)):
+        v = r(n).to(dt)
+        assert torch.equal(ops.relu2_(v.to(DEV)).cpu(), (torch.relu(v.float()) ** 2).to(dt))
     # keys: norm, rotation of the first 6 of 10 dimensions with scaled positions, raw keys as values
     nq, nkv, d, rot, page = 4, 2, 10, 6, 4
     qkv = r(5, (nq + nkv) * d)

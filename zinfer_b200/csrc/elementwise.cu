@@ -893,6 +893,48 @@ norm_residual_rows_kernel(float* __restrict__ h, const TA* __restrict__ a, const
   }
 }
 
+// Many rows whose updates come whole (no partial sums) and whose width is a multiple of 4 up to 8,192: 16-byte
+// accesses, the row's update read once and kept in registers between the sum of squares and the add.
+template <typename TA, typename TB, typename TO, bool HAS_B>
+__global__ void __launch_bounds__(256)
+norm_residual_vec_kernel(float* __restrict__ h, const TA* __restrict__ a, float sa, const TB* __restrict__ b, float sb,
+                         const float* __restrict__ w, float eps, TO* __restrict__ x_out, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  constexpr int MAXV = 8;                 // 4-wide pieces per thread
+  const size_t row = (size_t)blockIdx.x * H;
+  float4 y[MAXV];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int c = (i * 256 + threadIdx.x) * 4;
+    y[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < H) {
+      const float4 va = Vec4<TA>::load(a + row + c);
+      y[i] = make_float4(sa * va.x, sa * va.y, sa * va.z, sa * va.w);
+      if (HAS_B) {
+        const float4 vb = Vec4<TB>::load(b + row + c);
+        y[i] = make_float4(fmaf(sb, vb.x, y[i].x), fmaf(sb, vb.y, y[i].y), fmaf(sb, vb.z, y[i].z), fmaf(sb, vb.w, y[i].w));
+      }
+      ss = fmaf(y[i].x, y[i].x, fmaf(y[i].y, y[i].y, fmaf(y[i].z, y[i].z, fmaf(y[i].w, y[i].w, ss))));
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int c = (i * 256 + threadIdx.x) * 4;
+    if (c < H) {
+      const float4 hv = Vec4<float>::load(h + row + c), wv = Vec4<float>::load(w + c);
+      const float4 v = make_float4(hv.x + y[i].x * inv * wv.x, hv.y + y[i].y * inv * wv.y, hv.z + y[i].z * inv * wv.z,
+                                   hv.w + y[i].w * inv * wv.w);
+      Vec4<float>::store(h + row + c, v);
+      if (x_out) Vec4<TO>::store(x_out + row + c, v);
+    }
+  }
+}
+
 // Few rows (a decode step): a row's loads are spread over up to 1024 threads, four columns of a thread in flight
 // together, and the summed update is kept in shared memory so that partial sums are read once.
 template <typename TA, typename TB, typename TO>
@@ -948,8 +990,17 @@ extern "C" int zi_norm_residual(float* h, const void* a, int a_dtype, const floa
   if (smem > 200 * 1024) return zi_refuse("norm_residual: rows of %d values are more than this kernel holds", H);
   // few rows (a decode step): a row's loads are spread over as many threads as it has columns in fours; many rows fill the GPU anyway
   const int threads = H >= 4096 ? 1024 : (H >= 2048 ? 512 : 256);
+  auto al16 = [](const void* p) { return p == nullptr || ((uintptr_t)p & 15) == 0; };
+  const bool vec = a && !a_part && !b_part && H % 4 == 0 && H <= 8192 && al16(h) && al16(a) && al16(b) && al16(w) && al16(x_out);
 #define ZI_NR(TA, TB, TO)                                                                                               \
   do {                                                                                                                  \
+    if (T > 512 && vec) {                                                                                               \
+      if (b) zi_launch(norm_residual_vec_kernel<TA, TB, TO, true>, dim3(T), dim3(256), 0, stream, h, (const TA*)a, sa,  \
+                       (const TB*)b, sb, w, eps, (TO*)x_out, H);                                                        \
+      else zi_launch(norm_residual_vec_kernel<TA, TB, TO, false>, dim3(T), dim3(256), 0, stream, h, (const TA*)a, sa,   \
+                     (const TB*)b, sb, w, eps, (TO*)x_out, H);                                                          \
+      break;                                                                                                            \
+    }                                                                                                                   \
     if (T > 512) {                                                                                                      \
       zi_launch(norm_residual_rows_kernel<TA, TB, TO>, dim3(T), dim3(256), 0, stream, h, (const TA*)a, a_part, a_splits, \
                 (size_t)a_zstride, sa, (const TB*)b, b_part, b_splits, (size_t)b_zstride, sb, w, eps, (TO*)x_out, H);   \
@@ -994,8 +1045,25 @@ __global__ void relu2_kernel(T* __restrict__ x, size_t n) {
   }
 }
 
+template <typename T>
+__global__ void relu2_vec_kernel(T* __restrict__ x, size_t n4) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n4) {
+    float4 v = Vec4<T>::load(x + 4 * i);
+    v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
+    Vec4<T>::store(x + 4 * i, make_float4(v.x * v.x, v.y * v.y, v.z * v.z, v.w * v.w));
+  }
+}
+
 extern "C" int zi_relu2(void* x, int dtype, long long n, cudaStream_t stream) {
   if (n <= 0) return 0;
+  if (n % 4 == 0 && ((uintptr_t)x & 15) == 0) {
+    const size_t n4 = (size_t)n / 4;
+    ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(relu2_vec_kernel<TT>, dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, stream, (TT*)x, n4));
+    return zi_check_launch("relu2");
+  }
   ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(relu2_kernel<TT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (TT*)x, (size_t)n));
   return zi_check_launch("relu2");
 }
