@@ -215,6 +215,27 @@ def test_long_decoding_and_first_tokens(model_dirs, dtype):
     assert len(first) == 3
 
 
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_decode_steps_from_graphs_with_the_separate_attention_kernels(model_dirs, name, monkeypatch):
+    """Single-token steps replayed from CUDA graphs with the decode attention that is NOT fused with the key's norm,
+    rotation and page write (what a step takes once it has more (request, kv head) pairs than twice the SMs): a long
+    prompt, then tokens one by one, against the plain model.  The kernels of such a step run back to back, each
+    starting while the one before it drains; the attention must not read a page before the kernel that writes the
+    newest key is done."""
+    from zinfer_b200 import ops
+    from zinfer_b200.engine import ModelRunner
+
+    monkeypatch.setattr(ops, "decode_fused_ok", lambda *a, **k: False)
+    d = model_dirs[(name, "bfloat16")]
+    cfg, w = P.load_model(d)
+    reqs = ru.make_requests(cfg["vocab_size"], [520], seed=13)
+    runner = ModelRunner.from_model_dir(d, dtype=torch.bfloat16, device=DEV, page_size=PAGE_SIZE[name], max_tokens=576)
+    got = ru.run_in_process(runner, ru.trace_tail_decode(reqs, 40))
+    assert runner.graphs is not None and runner.graphs.replays > 30
+    ru.assert_close(got, ru.plain_logits(cfg, w, reqs), what=f"separate decode attention from graphs ({name})", argmax_frac=0.8,
+                    rtol=1.2e-2, atol=1e-3)
+
+
 # ----------------------------------------------------------------------- sampling
 def _sample_many(logits_row, n, **kw):
     from zinfer_b200 import ops

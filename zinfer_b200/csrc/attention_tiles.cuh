@@ -419,10 +419,11 @@ __device__ __forceinline__ void attn_decode_unit(
     else
       load_kv_rows_pg<D>(ks, ks + ROWS_BYTES, key0, pg, kcache, vcache, nkv, kvh, page_size, page_shift, lane);
   };
-  // Not fused: the kernel before this one wrote the newest token's key and value (and q).  The first
-  // tiles are asked for before the wait for it unless they may hold that key.
-  const bool early = !FUSED && !XP && kt0 + (t_begin + STAGES - 1) * DC_TILE <= pos;
-  if (!FUSED && !early) pdl_wait();
+  // Not fused: the kernel before this one wrote the newest token's key and value (and q), so this kernel waits
+  // for it before it asks for any tile.  (Asking for the first tiles before the wait, on the ground that they
+  // cannot hold the newest key, gave wrong results when the steps ran back to back from a CUDA graph; the fused
+  // form, which no kernel of the step writes keys ahead of, does ask early.)
+  if (!FUSED) pdl_wait();
   int pg_next = lookup(0);
 #pragma unroll
   for (int t = 0; t < STAGES - 1; ++t) {
@@ -432,7 +433,6 @@ __device__ __forceinline__ void attn_decode_unit(
     if constexpr (!TMA) cp_async_commit();
   }
   if (!FUSED && TR) {
-    if (early) pdl_wait();
     const int hq = lane >> 2;   // the head (column of Q^T) this lane holds
     const bf16* qp = q + (size_t)token * q_stride + (size_t)(kvh * g + hq) * D + 2 * (lane & 3);
 #pragma unroll
@@ -442,7 +442,6 @@ __device__ __forceinline__ void attn_decode_unit(
     }
   }
   if (!FUSED && !TR) {
-    if (early) pdl_wait();
     const int r0 = lane >> 2, r1 = r0 + 8;
     const bf16* q0p = q + (size_t)token * q_stride + (size_t)(kvh * g + r0) * D + 2 * (lane & 3);
     const bf16* q1p = q + (size_t)token * q_stride + (size_t)(kvh * g + r1) * D + 2 * (lane & 3);
