@@ -433,7 +433,7 @@ def test_decode_attention_both_tile_forms(nq, nkv, d, page, window):
     o.require_kernel_status_ok("decode attention")
 
 
-@pytest.mark.parametrize("nq,nkv,d,page,window", [(6, 1, 64, 16, None), (32, 8, 128, 16, None), (6, 1, 64, 8, 37),
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(12, 2, 64, 16, None), (32, 8, 128, 16, None), (7, 1, 64, 8, 37),
                                                    (2, 1, 256, 16, None), (5, 5, 64, 16, 200), (24, 2, 128, 32, None)])
 def test_attention_with_a_sink_on_the_tensor_cores(nq, nkv, d, page, window):
     """A softmax whose denominator counts a sink (keys of score 0 without a value), by the tensor-core kernels whose
