@@ -276,6 +276,31 @@ def test_far_keys_page_edges_and_long_memory(tmp_path, dtype):
 
 
 @gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dim,heads,kv_heads", [(64, 4, 2), (128, 3, 1)])
+def test_attention_heads_the_tensor_core_kernels_take(tmp_path, dtype, dim, heads, kv_heads):
+    """Heads of 64 and 128: in bfloat16 the attention with its sink runs on the tensor-core kernels (prompt portions and
+    single tokens, the latter replayed from CUDA graphs with key splits), in float32 on the exact kernel; both against
+    the plain model, over prompts of hundreds of tokens, portions across page edges and long decoding."""
+    cfg = U.config(151, 96, [
+        U.layer(U.par(U.att(heads, kv_heads, dim, 0.4, dim // 2, base=5000.0, factor=2.0), U.delta(2, 1, 16, 24, 4), 0.9, 0.4), U.dense(64)),
+        U.layer(U.gla(2, 32, 16, 16.0), None),
+        U.layer(U.par(U.att(heads, kv_heads, dim, 0.4, dim // 2, base=5000.0, factor=2.0), U.delta(2, 1, 16, 24, 4), 0.9, 0.4), None),
+    ])
+    weights = U.make_weights(cfg, seed=71)
+    reqs = ru.make_requests(cfg["vocab"], [290, 150, 1], seed=10)
+    plain = U.plain_logits(cfg, weights, reqs)
+    runner = make_runner(tmp_path, cfg, weights, dtype, DEV, page_size=16, max_tokens=512, max_requests=3, poison_freed_pages=True)
+    edges = (16, 15, 1, 17, 31, 2, 130, 33, 47, 64, 1, 1, 14)
+    for mode, trace in (("whole", ru.trace_whole(reqs)), ("edges", ru.trace_portions(reqs, 0, sizes=edges)),
+                        ("long decode", ru.trace_tail_decode(reqs, 70)), ("mixed", ru.trace_mixed(reqs, 3, max_live=3, tail=20))):
+        got = ru.run_in_process(runner, trace)
+        ru.assert_close(got, plain, what=f"heads of {dim}/{mode}", argmax_frac=0.0, **TOL[dtype])
+    assert runner.graphs is not None and runner.graphs.replays > 60
+    runner.manager.check()
+
+
+@gpu
 def test_long_memory_is_real_and_a_lost_state_would_show(tmp_path):
     """With slowly forgetting recurrences the first token still moves the logits 200 tokens later by a hundred times
     the float32 tolerance (so a state that is lost, reset or taken from another slot cannot pass), and the engine
